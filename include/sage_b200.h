@@ -1,0 +1,121 @@
+/* C-ABI of libsage_b200.so: the quantize-then-attend hot path for NVIDIA B200 (sm_100a).
+ *
+ * Plain pointers and sizes only; no torch types, no C++ exceptions across the boundary.  Every
+ * function returns 0 on success or a negative SAGE_E_* code, and `sage_last_error()` then returns a
+ * one-line description (thread-local).  All pointers except `strides` arrays are DEVICE pointers.
+ * All work is enqueued on `stream` (a cudaStream_t passed as void*, NULL = default stream); nothing
+ * synchronises, nothing allocates: the caller owns every buffer, as in the reference, where the
+ * Python side allocates with torch.empty and hands raw pointers to extern "C" kernels.
+ *
+ * Citations below are paths inside the reference project (IxMxAMAR/SageAttention-RDNA4).
+ */
+#ifndef SAGE_B200_H
+#define SAGE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define SAGE_HEAD_DIM 128        /* the only head_dim the hand-written path serves            */
+#define SAGE_TILE 128            /* query tile and key tile; key length is padded to this     */
+
+enum { SAGE_F16 = 0, SAGE_BF16 = 1 };            /* element type of q, k, v and of the output  */
+enum { SAGE_QK_INT8 = 0, SAGE_QK_E4M3 = 1 };     /* code type of the quantised Q and K         */
+
+enum {
+  SAGE_OK = 0,
+  SAGE_E_ARG = -1,        /* contract violation: null pointer, bad size, misaligned pointer    */
+  SAGE_E_UNSUPPORTED = -2,/* valid request this build does not serve                           */
+  SAGE_E_CUDA = -3,       /* a CUDA runtime/driver call failed; see sage_last_error()          */
+  SAGE_E_WORKSPACE = -4   /* workspace too small                                               */
+};
+
+/* Library version (major*10000 + minor*100 + patch). */
+int sage_version(void);
+
+/* Description of the last failure on the calling thread ("" if none). */
+const char* sage_last_error(void);
+
+/* Padded key length: N rounded up to SAGE_TILE.  Replaces `n_pad = ceil(N/64)*64`
+ * (sageattention/sk1_backend/hip_prologue.py:93-95); the tile here is 128 keys. */
+int64_t sage_pad_len(int64_t n);
+
+/* Bytes of the control block `ctrl` the prologue needs for B*H heads (mean partial sums, per-head
+ * arrival counters, per-head running max of the V scale).  256-byte aligned device memory. */
+size_t sage_prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
+
+/* The quantisation prologue: Q, K, V -> Q8, SQ, K8, SK, V8T, SV, SVP, S (and MEAN).
+ *
+ * Replaces HipPrologue.quant_kv (sageattention/sk1_backend/hip_prologue.py:188-244, kernels
+ * h34_kseq_mean_* and h34_quant_kv_* in kernels/hip/h34_prologue.hip:91-294), the in-kernel Q
+ * quantisation of the attention kernels (kernels/hip/sk1_t6i.hip:91-117,
+ * kernels/hip/sk1_t4a1sb.hip:73-100) and fold_v_scale
+ * (sageattention/sk1_backend/__init__.py:561-579).
+ *
+ *   q, k, v   logical (B,H,N,128) fp16/bf16 views; q_strides/k_strides/v_strides give the
+ *             (batch, head, row) strides in ELEMENTS; the last axis is contiguous; every stride is
+ *             a multiple of 8 and every base pointer 16-byte aligned.
+ *   q8        (B*H, N, 128)      int8 | e4m3 codes of Q, one scale per token
+ *   sq        (B*H, N)           fp32 dequant scale of Q: amax/127 (int8) or amax/448 (e4m3)
+ *   k8        (B*H, N_pad, 128)  codes of K - mean; pad rows 0
+ *   sk        (B*H, N_pad)       fp32 scale of K; pad rows 1.0
+ *   v8t       (B*H, 128, N_pad)  e4m3 codes of V, transposed; pad columns 0
+ *   sv        (B*H, N_pad)       fp32 scale of V; pad rows 0.0
+ *   svp       (B*H, N_pad)       fp32 staged factor  fl(fl(sv / S) * 448)
+ *   s_fold    (B*H)              S = max(max_n sv, 1)
+ *   mean      (B*H, 128)         fp32 sequence mean of K (written only when smooth_k != 0)
+ *   ctrl      sage_prologue_ctrl_bytes() of scratch; contents need not be initialised
+ *   N_pad     must equal sage_pad_len(N)
+ * Two kernel launches (mean, quantise) and one small memset. */
+int sage_prologue(const void* q, const void* k, const void* v,
+                  void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
+                  float* s_fold, float* mean, void* ctrl,
+                  int64_t B, int64_t H, int64_t N, int64_t N_pad,
+                  const int64_t q_strides[3], const int64_t k_strides[3],
+                  const int64_t v_strides[3],
+                  int dtype, int qk_mode, int smooth_k, void* stream);
+
+/* The attention kernel on quantised operands.
+ *
+ * Replaces Sk1Attn.launch / launch_strided (sageattention/sk1_backend/sk1_loader.py:628-688) and
+ * the kernels sk1t6i_attn_fwd_c0/_c1 (kernels/hip/sk1_t6i.hip:69-316) and
+ * sk1t4a1sb_attn_fwd_c0/_c1 (kernels/hip/sk1_t4a1sb.hip:51-308).
+ *
+ *   out        logical (B,H,N,128) fp16/bf16 view with (batch, head, row) ELEMENT strides
+ *              o_strides, last axis contiguous, strides multiples of 8, 16-byte aligned base.
+ *   status     one int32 in device memory, zero before the call; the kernel ORs in a non-zero
+ *              code if one of its bounded waits gave up (the output is then undefined).
+ * The operands are the prologue's outputs for the same B, H, N, N_pad, qk_mode. */
+int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* sk,
+                  const void* v8t, const float* svp, const float* s_fold, void* out,
+                  int64_t B, int64_t H, int64_t N, int64_t N_pad, const int64_t o_strides[3],
+                  int causal, float sm_scale, int out_dtype, int qk_mode,
+                  int32_t* status, void* stream);
+
+/* Bytes of workspace `sage_attention` needs for one call (all intermediates + ctrl + status). */
+size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N);
+
+/* The whole call: prologue + attention, the path `sageattn` takes
+ * (sageattention/sk1_backend/__init__.py:982-1284, try_sk1_t1).  `workspace` is
+ * sage_workspace_bytes() of 256-byte aligned device memory owned by the caller.  qk_mode follows
+ * the reference's default when negative: int8 for fp16 inputs, e4m3 for bf16. */
+int sage_attention(const void* q, const void* k, const void* v, void* out,
+                   void* workspace, size_t workspace_bytes,
+                   int64_t B, int64_t H, int64_t N,
+                   const int64_t q_strides[3], const int64_t k_strides[3],
+                   const int64_t v_strides[3], const int64_t o_strides[3],
+                   int dtype, int qk_mode, int causal, int smooth_k, float sm_scale,
+                   void* stream);
+
+/* Offsets (bytes from `workspace`) of the intermediates sage_attention uses, for callers and
+ * tests that want to look at them: order q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status.
+ * Returns the number of entries written (11). */
+int sage_workspace_layout(int64_t B, int64_t H, int64_t N, size_t offsets[11]);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SAGE_B200_H */

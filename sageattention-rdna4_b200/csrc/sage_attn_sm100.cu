@@ -1,0 +1,532 @@
+// Quantised flash attention for B200 (sm_100a): tcgen05 tensor cores, TMEM accumulators, TMA tiles.
+//
+// One CTA owns 128 queries of one (batch, head) and streams 128-key tiles; two CTAs share an SM so
+// that one CTA's softmax overlaps the other's matrix products.  Roles inside a CTA (192 threads):
+//   warp 0     TMA producer: Q tile once, then a 2-deep ring of K tiles and a 2-deep ring of
+//              V^T tiles, each V stage carrying that tile's 128 K scales and 128 staged V factors
+//   warp 1     allocates 256 TMEM columns; one thread issues every tcgen05.mma
+//   warps 2-5  softmax: thread r owns query row r of the tile (TMEM lane r)
+// Per key tile j:
+//   S  = Q8 . K8^T          kind::i8 (s32) or kind::f8f6f4 (f32), M=N=K=128, into TMEM cols 0..127
+//   s  = f32(S) * (c_q * sk[key])   (log2 domain), mask, row max, alpha = exp2(m_old - m_new)
+//   O *= alpha in TMEM when some row's max moved; l = l*alpha + sum(p), p = exp2(s - m)
+//   P8 = e4m3(p * svp[key]) written to shared memory in the 128-byte swizzled K-major layout
+//   O += P8 . V8            kind::f8f6f4 into TMEM cols 128..255
+// Epilogue: out = O * (S_fold / (l * 448)) -> fp16 / bf16.
+// (numerics: kernels/hip/sk1_t6i.hip:151-299 and kernels/hip/sk1_t4a1sb.hip:176-189 of the
+// reference, with a 128-key instead of a 64-key tile for the running max)
+//
+// Every wait on an mbarrier is bounded: after about two seconds, or as soon as another CTA has
+// reported a failure, the waiter records a code in the status word, the CTA drains and frees its
+// TMEM, and CTAs that start later return at once.
+#include <cuda.h>
+
+#include "sage_common.cuh"
+#include "sage_internal.h"
+
+namespace sage {
+
+constexpr int ATT_THREADS = 192;
+constexpr uint32_t TILE_BYTES = TILE * HD;          // 16 KiB: 128 rows x 128 one-byte codes
+constexpr uint32_t VEC_BYTES = TILE * 4;            // 128 floats
+constexpr uint32_t OFF_Q = 0;
+constexpr uint32_t OFF_K = OFF_Q + TILE_BYTES;      // 2 stages
+constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;  // 2 stages
+constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;
+constexpr uint32_t OFF_SK = OFF_P + TILE_BYTES;     // 2 stages of K scales
+constexpr uint32_t OFF_SV = OFF_SK + 2 * VEC_BYTES; // 2 stages of staged V factors
+constexpr uint32_t OFF_BAR = OFF_SV + 2 * VEC_BYTES;
+constexpr uint32_t OFF_MISC = OFF_BAR + 128;
+constexpr uint32_t SMEM_USED = OFF_MISC + 64;
+constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;   // slack for the 1024-byte alignment
+constexpr uint32_t TMEM_COLS = 256;
+constexpr uint32_t TMEM_O = 128;
+
+enum Bar { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SFREE = 10,
+           BAR_PF = 11, BAR_PV = 12, BAR_COUNT = 13 };
+
+enum { ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_SOFTMAX = 4 };
+
+constexpr long long WAIT_CYCLES = 4000000000LL;      // about two seconds of SM clock
+
+// ------------------------------------------------------------------------------------------------
+// PTX wrappers
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+  return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+// Bounded wait.  Returns false when it gave up (its own time limit, or a failure flagged by
+// someone else); the caller then leaves its loop.
+__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* cta_abort,
+                                            int32_t* status, int code) {
+  const long long t0 = clock64();
+  uint32_t it = 0;
+  for (;;) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((++it & 255u) == 0u) {
+      if (*cta_abort) return false;
+      if (*reinterpret_cast<volatile int32_t*>(status) != 0) { *cta_abort = 1u; return false; }
+      if (clock64() - t0 > WAIT_CYCLES) {
+        atomicOr(status, code);
+        *cta_abort = 1u;
+        return false;
+      }
+    }
+  }
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* cta_abort,
+                                          int32_t* status, int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  return mbar_wait_slow(bar, parity, cta_abort, status, code);
+}
+
+__device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
+                                            int c0, int c1, int c2) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void prefetch_map(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+template <bool INT8>
+__device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                       uint32_t accumulate) {
+  if (INT8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+
+// 32 lanes x 32 columns of 32-bit: thread t of the warp receives columns col..col+31 of its lane.
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
+        "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+
+__device__ __forceinline__ float ex2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// Shared-memory matrix descriptor of a K-major tile of 128-byte rows written with the 128-byte
+// swizzle (what TMA SWIZZLE_128B produces): 8-row groups 1024 bytes apart, descriptor version 1.
+__device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor: D format at bit 4, A/B formats at bits 7/10, N>>3 at bit 17, M>>4 at 24.
+constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+constexpr uint32_t IDESC_F8 = (1u << 4) | (0u << 7) | (0u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
+
+struct AttnKArgs {
+  const float *sq, *sk, *svp, *s_fold;
+  void* out;
+  long long N, N_pad, H;
+  long long o_sb, o_sh, o_sr;
+  float sm_scale;
+  int32_t* status;
+};
+
+template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+  __half2 h = __floats2half2_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+  __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+  return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// ------------------------------------------------------------------------------------------------
+// The kernel.  grid (ceil(N/128), B*H), block 192, two CTAs per SM.
+// ------------------------------------------------------------------------------------------------
+template <bool INT8, bool CAUSAL, typename OutT>
+__global__ void __launch_bounds__(ATT_THREADS, 2)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* gbase = smem_raw + (base - raw_addr);
+  const uint32_t bar0 = base + OFF_BAR;
+  volatile uint32_t* misc = reinterpret_cast<volatile uint32_t*>(gbase + OFF_MISC);  // [0] tmem, [1] abort
+  volatile uint32_t* cta_abort = misc + 1;
+  auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
+
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int q_tile = CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // longest first
+  const int bh = blockIdx.y;
+  const int n_tiles = CAUSAL ? (q_tile + 1) : (int)(a.N_pad / TILE);
+
+  if (tid == 0) {
+    mbar_init(bar(BAR_Q), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(bar(BAR_KF + s), 1);
+      mbar_init(bar(BAR_KE + s), 1);
+      mbar_init(bar(BAR_VF + s), 1);
+      mbar_init(bar(BAR_VE + s), 1);
+    }
+    mbar_init(bar(BAR_SF), 1);
+    mbar_init(bar(BAR_SFREE), 4);
+    mbar_init(bar(BAR_PF), 4);
+    mbar_init(bar(BAR_PV), 1);
+    misc[1] = (*reinterpret_cast<volatile int32_t*>(a.status) != 0) ? 1u : 0u;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                 ::"r"(base + OFF_MISC), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = misc[0];
+  const bool skip_all = misc[1] != 0u;
+
+  if (!skip_all) {
+    if (warp == 0) {
+      // ------------------------------- TMA producer -------------------------------
+      if (lane == 0) {
+        prefetch_map(&tm_q); prefetch_map(&tm_k); prefetch_map(&tm_v);
+        mbar_expect_tx(bar(BAR_Q), TILE_BYTES);
+        tma_load_3d(base + OFF_Q, &tm_q, bar(BAR_Q), 0, q_tile * TILE, bh);
+        const float* sk_row = a.sk + (size_t)bh * a.N_pad;
+        const float* sv_row = a.svp + (size_t)bh * a.N_pad;
+        for (int j = 0; j < n_tiles; ++j) {
+          const int s = j & 1;
+          const uint32_t par = ((uint32_t)(j >> 1) & 1u) ^ 1u;
+          if (!mbar_wait(bar(BAR_KE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
+          mbar_expect_tx(bar(BAR_KF + s), TILE_BYTES);
+          tma_load_3d(base + OFF_K + s * TILE_BYTES, &tm_k, bar(BAR_KF + s), 0, j * TILE, bh);
+          if (!mbar_wait(bar(BAR_VE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
+          mbar_expect_tx(bar(BAR_VF + s), TILE_BYTES + 2 * VEC_BYTES);
+          tma_load_3d(base + OFF_V + s * TILE_BYTES, &tm_v, bar(BAR_VF + s), j * TILE, 0, bh);
+          bulk_load(base + OFF_SK + s * VEC_BYTES, sk_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_VF + s));
+          bulk_load(base + OFF_SV + s * VEC_BYTES, sv_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_VF + s));
+        }
+      }
+    } else if (warp == 1) {
+      // ------------------------------- MMA issuer ---------------------------------
+      if (lane == 0) {
+        constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
+        bool ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
+        for (int j = 0; ok && j <= n_tiles; ++j) {
+          if (j < n_tiles) {
+            const int s = j & 1;
+            ok = mbar_wait(bar(BAR_KF + s), (uint32_t)(j >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok && j > 0) ok = mbar_wait(bar(BAR_SFREE), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_ss<INT8>(tmem, kmajor_sw128_desc(base + OFF_Q + 32 * k),
+                           kmajor_sw128_desc(base + OFF_K + s * TILE_BYTES + 32 * k), IDESC_QK, k > 0);
+            tc_commit(bar(BAR_KE + s));
+            tc_commit(bar(BAR_SF));
+          }
+          if (j > 0) {
+            const int jj = j - 1, s = jj & 1;
+            ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(jj >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok) ok = mbar_wait(bar(BAR_PF), (uint32_t)jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_ss<false>(tmem + TMEM_O, kmajor_sw128_desc(base + OFF_P + 32 * k),
+                            kmajor_sw128_desc(base + OFF_V + s * TILE_BYTES + 32 * k), IDESC_F8,
+                            (jj > 0 || k > 0) ? 1u : 0u);
+            tc_commit(bar(BAR_VE + s));
+            tc_commit(bar(BAR_PV));
+          }
+        }
+      }
+    } else {
+      // ------------------------------- softmax warps ------------------------------
+      const int row = 32 * (warp & 3) + lane;               // TMEM lane == query row of the tile
+      const long long q_row = (long long)q_tile * TILE + row;
+      const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+      const float cq = (q_row < a.N)
+          ? __fmul_rn(__fmul_rn(a.sm_scale, LOG2E_F), __ldg(a.sq + (size_t)bh * a.N + q_row)) : 0.f;
+      float m = -INFINITY, l = 0.f;
+      bool ok = true;
+      uint8_t* p_row = gbase + OFF_P + row * 128;
+      const int swz = row & 7;
+
+      for (int j = 0; j < n_tiles; ++j) {
+        const int s = j & 1;
+        ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(j >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        if (ok) ok = mbar_wait(bar(BAR_SF), (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        tc_fence_after();
+        uint32_t acc[TILE];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) tmem_ld32(t_lane + 32 * i, acc + 32 * i);
+        tmem_ld_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_SFREE));
+
+        const float4* skv = reinterpret_cast<const float4*>(gbase + OFF_SK + s * VEC_BYTES);
+        const float4* svv = reinterpret_cast<const float4*>(gbase + OFF_SV + s * VEC_BYTES);
+        float sc[TILE];
+#pragma unroll
+        for (int k4 = 0; k4 < TILE / 4; ++k4) {
+          const float4 kk = skv[k4];
+          const float ks[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int k = 4 * k4 + e;
+            const float x = INT8 ? (float)(int)acc[k] : __uint_as_float(acc[k]);
+            sc[k] = x * (cq * ks[e]);
+          }
+        }
+        // Tile-uniform mask: the diagonal tile when causal, the ragged last tile otherwise.
+        if (CAUSAL) {
+          if (j == q_tile) {
+#pragma unroll
+            for (int k = 0; k < TILE; ++k) if (k > row) sc[k] = -INFINITY;
+          }
+        } else {
+          if ((long long)(j + 1) * TILE > a.N) {
+            const int live = (int)(a.N - (long long)j * TILE);
+#pragma unroll
+            for (int k = 0; k < TILE; ++k) if (k >= live) sc[k] = -INFINITY;
+          }
+        }
+        float mx = sc[0];
+#pragma unroll
+        for (int k = 1; k < TILE; ++k) mx = fmaxf(mx, sc[k]);
+        const float m_new = fmaxf(m, mx);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = ex2(m - m_use);
+
+        if (j > 0) {
+          ok = mbar_wait(bar(BAR_PV), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+          if (__any_sync(0xffffffffu, m_new > m)) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint32_t o[32];
+              tmem_ld32(t_lane + TMEM_O + 32 * i, o);
+              tmem_ld_wait();
+#pragma unroll
+              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+              tmem_st32(t_lane + TMEM_O + 32 * i, o);
+            }
+            tmem_st_wait();
+          }
+        }
+        m = m_new;
+
+        float psum = 0.f;
+#pragma unroll
+        for (int cc = 0; cc < 8; ++cc) {                    // 16 keys = one 16-byte chunk of the P row
+          uint32_t w[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g) {
+            const float4 vv = svv[4 * cc + g];
+            const float p0 = ex2(sc[16 * cc + 4 * g + 0] - m_use);
+            const float p1 = ex2(sc[16 * cc + 4 * g + 1] - m_use);
+            const float p2 = ex2(sc[16 * cc + 4 * g + 2] - m_use);
+            const float p3 = ex2(sc[16 * cc + 4 * g + 3] - m_use);
+            psum += (p0 + p1) + (p2 + p3);
+            w[g] = e4m3x4(p0 * vv.x, p1 * vv.y, p2 * vv.z, p3 * vv.w);
+          }
+          *reinterpret_cast<uint4*>(p_row + ((cc ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
+        l = l * alpha + psum;
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_PF));
+      }
+
+      // ------------------------------- epilogue -----------------------------------
+      if (ok) {
+        ok = mbar_wait(bar(BAR_PV), (uint32_t)(n_tiles - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+      }
+      if (ok) {
+        tc_fence_after();
+        const float S = __ldg(a.s_fold + bh);
+        const float inv = (l > 0.f) ? __fdiv_rn(S, __fmul_rn(l, F8_MAX)) : 0.f;
+        const long long b = bh / a.H, h = bh - b * a.H;
+        OutT* orow = reinterpret_cast<OutT*>(a.out) + b * a.o_sb + h * a.o_sh + q_row * a.o_sr;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          uint32_t o[32];
+          tmem_ld32(t_lane + TMEM_O + 32 * i, o);
+          tmem_ld_wait();
+          if (q_row < a.N) {
+#pragma unroll
+            for (int g = 0; g < 4; ++g) {
+              uint4 w;
+              w.x = pack2<OutT>(__uint_as_float(o[8 * g + 0]) * inv, __uint_as_float(o[8 * g + 1]) * inv);
+              w.y = pack2<OutT>(__uint_as_float(o[8 * g + 2]) * inv, __uint_as_float(o[8 * g + 3]) * inv);
+              w.z = pack2<OutT>(__uint_as_float(o[8 * g + 4]) * inv, __uint_as_float(o[8 * g + 5]) * inv);
+              w.w = pack2<OutT>(__uint_as_float(o[8 * g + 6]) * inv, __uint_as_float(o[8 * g + 7]) * inv);
+              *reinterpret_cast<uint4*>(orow + 32 * i + 8 * g) = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // Teardown: every role has left its loop (all waits are bounded).  After a failure give copies
+  // still in flight a moment to land before the shared memory is released.
+  tc_fence_before();
+  __syncthreads();
+  if (*cta_abort) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 400000) { }
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side: tensor maps and launch.
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+
+// 3-D map over one-byte codes: dims (inner, rows, heads), box 128 x 128 x 1, 128-byte swizzle,
+// out-of-range elements read as zero.
+static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t rows, uint64_t heads,
+                     uint64_t row_stride_bytes, uint64_t head_stride_bytes) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[3] = {inner, rows, heads};
+  cuuint64_t strides[2] = {row_stride_bytes, head_stride_bytes};
+  cuuint32_t box[3] = {128, 128, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  return fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+template <bool INT8, bool CAUSAL, typename OutT>
+static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
+                               const AttnKArgs& ka, dim3 grid, cudaStream_t st) {
+  auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT>;
+  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  if (e != cudaSuccess) return e;
+  kern<<<grid, ATT_THREADS, SMEM_BYTES, st>>>(mq, mk, mv, ka);
+  return cudaGetLastError();
+}
+
+cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why) {
+  const uint64_t bh = (uint64_t)(p.B * p.H), N = (uint64_t)p.N, N_pad = (uint64_t)p.N_pad;
+  CUtensorMap mq, mk, mv;
+  if (!make_map(&mq, p.q8, HD, N, bh, HD, N * HD) ||
+      !make_map(&mk, p.k8, HD, N_pad, bh, HD, N_pad * HD) ||
+      !make_map(&mv, p.v8t, N_pad, HD, bh, N_pad, N_pad * HD)) {
+    if (why) *why = "cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)";
+    return cudaErrorInvalidValue;
+  }
+  AttnKArgs ka;
+  ka.sq = p.sq; ka.sk = p.sk; ka.svp = p.svp; ka.s_fold = p.s_fold; ka.out = p.out;
+  ka.N = p.N; ka.N_pad = p.N_pad; ka.H = p.H;
+  ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
+  ka.sm_scale = p.sm_scale; ka.status = p.status;
+  dim3 grid((unsigned)((p.N + TILE - 1) / TILE), (unsigned)bh);
+  const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
+  cudaError_t e;
+  switch (key) {
+    case 7: e = launch_inst<true, true, __half>(mq, mk, mv, ka, grid, st); break;
+    case 6: e = launch_inst<true, true, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
+    case 5: e = launch_inst<true, false, __half>(mq, mk, mv, ka, grid, st); break;
+    case 4: e = launch_inst<true, false, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
+    case 3: e = launch_inst<false, true, __half>(mq, mk, mv, ka, grid, st); break;
+    case 2: e = launch_inst<false, true, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
+    case 1: e = launch_inst<false, false, __half>(mq, mk, mv, ka, grid, st); break;
+    default: e = launch_inst<false, false, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
+  }
+  if (e != cudaSuccess && why) *why = "attention kernel launch failed";
+  return e;
+}
+
+}  // namespace sage

@@ -1,0 +1,76 @@
+// Shared device/host helpers of the B200 quantize-then-attend library.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+namespace sage {
+
+constexpr int HD = 128;        // head dim
+constexpr int TILE = 128;      // query tile == key tile == prologue token tile
+constexpr float I8_MAX = 127.0f;
+constexpr float F8_MAX = 448.0f;
+constexpr float SCALE_FLOOR = 1e-12f;
+constexpr float LOG2E_F = 1.4426950408889634f;
+
+// Control block of the prologue (device memory, zeroed by a memset at the start of every call).
+struct CtrlHeader {
+  // per head: [0] arrivals of the mean kernel, [1] arrivals of the quantiser, [2] max V scale bits
+  // laid out as three arrays of BH words; the fp64 partial sums follow at `partial_off`.
+  static __host__ __device__ inline size_t words(int64_t bh) { return (size_t)3 * (size_t)bh; }
+  static __host__ __device__ inline size_t partial_off(int64_t bh) {
+    return (words(bh) * 4 + 255) / 256 * 256;
+  }
+};
+
+// How many CTAs share one head's sequence in the mean kernel.
+inline int kmean_splits(int64_t bh, int64_t n) {
+  int64_t want = (4 * 148 + bh - 1) / bh;          // about four waves of CTAs on 148 SMs
+  int64_t cap = (n + 255) / 256;                   // at least 256 tokens per CTA
+  if (want > cap) want = cap;
+  if (want > 64) want = 64;
+  if (want < 1) want = 1;
+  return (int)want;
+}
+
+template <typename T> struct Elem;
+template <> struct Elem<__half> {
+  static __device__ __forceinline__ float2 cvt2(uint32_t w) {
+    return __half22float2(*reinterpret_cast<const __half2*>(&w));
+  }
+};
+template <> struct Elem<__nv_bfloat16> {
+  static __device__ __forceinline__ float2 cvt2(uint32_t w) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w));
+  }
+};
+
+// 16 bytes = 8 elements -> 8 floats (exact widening).
+template <typename T>
+__device__ __forceinline__ void unpack8(const uint4& u, float* x) {
+  float2 a = Elem<T>::cvt2(u.x), b = Elem<T>::cvt2(u.y), c = Elem<T>::cvt2(u.z), d = Elem<T>::cvt2(u.w);
+  x[0] = a.x; x[1] = a.y; x[2] = b.x; x[3] = b.y; x[4] = c.x; x[5] = c.y; x[6] = d.x; x[7] = d.y;
+}
+
+// Two floats -> two e4m3 bytes (a in the low byte), round to nearest even, saturating.
+__device__ __forceinline__ uint32_t e4m3x2(float a, float b) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, __NV_E4M3);
+}
+__device__ __forceinline__ uint32_t e4m3x4(float a, float b, float c, float d) {
+  return e4m3x2(a, b) | (e4m3x2(c, d) << 16);
+}
+
+// Round-half-even to int8 with the [-128, 127] clamp, four codes per word (a in the low byte).
+__device__ __forceinline__ uint32_t i8_rne(float y) {
+  int q = __float2int_rn(y);
+  q = max(-128, min(127, q));
+  return (uint32_t)q & 0xFFu;
+}
+__device__ __forceinline__ uint32_t i8x4(float a, float b, float c, float d) {
+  return i8_rne(a) | (i8_rne(b) << 8) | (i8_rne(c) << 16) | (i8_rne(d) << 24);
+}
+
+}  // namespace sage

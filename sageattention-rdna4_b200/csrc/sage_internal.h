@@ -1,0 +1,40 @@
+// Internal C++ interface between the C-ABI translation unit and the kernel translation units.
+#pragma once
+#include <cuda_runtime.h>
+#include <stddef.h>
+#include <stdint.h>
+
+namespace sage {
+
+struct PrologueParams {
+  const void *q, *k, *v;
+  void *q8, *k8, *v8t;
+  float *sq, *sk, *sv, *svp, *s_fold, *mean;
+  void* ctrl;
+  int64_t B, H, N, N_pad;
+  int64_t q_strides[3], k_strides[3], v_strides[3];   // (batch, head, row) in elements
+  int dtype;      // 0 fp16, 1 bf16
+  int qk_mode;    // 0 int8, 1 e4m3
+  int smooth_k;
+};
+
+struct AttnParams {
+  const void *q8, *k8, *v8t;
+  const float *sq, *sk, *svp, *s_fold;
+  void* out;
+  int64_t B, H, N, N_pad;
+  int64_t o_strides[3];                                // (batch, head, row) in elements
+  int causal;
+  float sm_scale;
+  int out_dtype;  // 0 fp16, 1 bf16
+  int qk_mode;    // 0 int8, 1 e4m3
+  int32_t* status;
+};
+
+cudaError_t launch_prologue(const PrologueParams& p, cudaStream_t st);
+size_t prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
+
+// Returns cudaSuccess or an error; `why` (if non-null) receives a static description on failure.
+cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why);
+
+}  // namespace sage

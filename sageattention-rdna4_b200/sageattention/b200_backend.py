@@ -1,0 +1,306 @@
+"""Host side of the B200 quantize-then-attend path: acceptance rules, buffer ownership, launches.
+
+Mirrors, for this one path, the reference's router `try_sk1_t1`
+(sageattention/sk1_backend/__init__.py:982-1284), its acceptance rule `strided_view_reason`
+(sageattention/sk1_backend/sk1_loader.py:313-369) and `_envelope_ok`
+(sageattention/sk1_backend/__init__.py:920-979), its prologue wrapper `HipPrologue.quant_kv`
+(sageattention/sk1_backend/hip_prologue.py:188-244) and its launcher `Sk1Attn.launch`
+(sageattention/sk1_backend/sk1_loader.py:628-688).  Differences that are deliberate: a request
+outside the envelope raises (there is no fallback path), Q is quantised in the prologue and its
+codes are materialised, keys are padded to 128, and the fold S is computed inside the prologue.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from collections import OrderedDict
+from typing import Dict, Optional, Tuple
+
+import torch
+
+from . import _native
+
+HEAD_DIM = 128
+TILE = 128
+_INT32_MAX = 2 ** 31 - 1
+
+#: Every reason `strided_view_reason` can return, in evaluation order (same strings as the reference).
+STRIDED_REFUSALS = ("rank", "stride_last", "stride_nonpos", "stride_align", "ptr_align",
+                    "stride_overlap", "stride_int32")
+
+_counters = {"calls": 0, "refusals": 0}
+_counters_lock = threading.Lock()
+
+
+def pad_len(n: int) -> int:
+    return (int(n) + TILE - 1) // TILE * TILE
+
+
+def strided_view_reason(t: torch.Tensor) -> Optional[str]:
+    """None if `t` is a servable logical (B,H,N,D) view, else the reason.  Same rule and order as
+    the reference: rank 4; last stride 1; strides positive; outer strides multiples of 8 elements;
+    16-byte aligned pointer; injective index map (dims of size > 1 sorted by stride must satisfy
+    stride[k+1] >= stride[k]*size[k]); strides below 2**31."""
+    if t.dim() != 4:
+        return "rank"
+    if int(t.stride(3)) != 1:
+        return "stride_last"
+    st = [int(s) for s in t.stride()]
+    if any(s <= 0 for s in st):
+        return "stride_nonpos"
+    if any(st[i] % 8 for i in (0, 1, 2)):
+        return "stride_align"
+    if int(t.data_ptr()) % 16:
+        return "ptr_align"
+    sh = [int(x) for x in t.shape]
+    dims = sorted((st[i], sh[i]) for i in range(4) if sh[i] > 1)
+    for (s0, n0), (s1, _n1) in zip(dims, dims[1:]):
+        if s1 < s0 * n0:
+            return "stride_overlap"
+    if any(s > _INT32_MAX for s in st):
+        return "stride_int32"
+    return None
+
+
+def envelope_reason(q, k, v, tensor_layout, return_lse=False, smooth_v=False, attn_mask=None,
+                    require_cuda=True) -> Optional[str]:
+    """None if the call is inside the envelope, else a short reason (the reference's strings:
+    layout, return_lse, attn_mask, smooth_v, device, dtype, rank, stride_*, ptr_align, head_dim,
+    batch, heads, seq_len).  head_dim 64 is refused here (the reference falls back for it)."""
+    if tensor_layout not in ("HND", "NHD"):
+        return "layout"
+    if return_lse:
+        return "return_lse"
+    if attn_mask is not None:
+        return "attn_mask"
+    if smooth_v:
+        return "smooth_v"
+    if require_cuda and not (q.is_cuda and k.is_cuda and v.is_cuda):
+        return "device"
+    if q.device != k.device or q.device != v.device:
+        return "device"
+    if not (q.dtype == k.dtype == v.dtype):
+        return "dtype"
+    if q.dtype not in (torch.float16, torch.bfloat16):
+        return "dtype"
+    if not (q.dim() == 4 and k.dim() == 4 and v.dim() == 4):
+        return "rank"
+    if tensor_layout == "NHD":
+        q, k, v = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    for t in (q, k, v):
+        r = strided_view_reason(t)
+        if r is not None:
+            return r
+    if q.size(3) != HEAD_DIM or k.size(3) != q.size(3) or v.size(3) != q.size(3):
+        return "head_dim"
+    if q.size(0) != k.size(0) or q.size(0) != v.size(0):
+        return "batch"
+    if q.size(1) != k.size(1) or q.size(1) != v.size(1):
+        return "heads"
+    if q.size(2) != k.size(2) or k.size(2) != v.size(2):
+        return "seq_len"
+    if q.size(2) < 1:
+        return "seq_len"
+    return None
+
+
+def _dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float16:
+        return _native.SAGE_F16
+    if dt == torch.bfloat16:
+        return _native.SAGE_BF16
+    raise ValueError("dtype must be float16 or bfloat16, got %s" % dt)
+
+
+def _bhr(t: torch.Tensor):
+    """(batch, head, row) element strides of a logical (B,H,N,D) view."""
+    return _native.strides3(t.stride(0), t.stride(1), t.stride(2))
+
+
+def _stream(device) -> ctypes.c_void_p:
+    return ctypes.c_void_p(int(torch.cuda.current_stream(device).cuda_stream))
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else int(t.data_ptr()))
+
+
+def _require_cuda(*ts):
+    for t in ts:
+        if not t.is_cuda:
+            raise ValueError("the B200 path serves CUDA tensors only (got a %s tensor); there is no CPU path"
+                             % t.device.type)
+
+
+def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool = True,
+              int8: Optional[bool] = None) -> Dict[str, torch.Tensor]:
+    """Run the prologue on logical (B,H,N,D) views and return every tensor it writes:
+    q8 (BH,N,D), sq (BH,N), k8 (BH,N_pad,D), sk (BH,N_pad), v8t (BH,D,N_pad), sv, svp (BH,N_pad),
+    S (BH,), mean (BH,D) or None.  `int8=None` follows the reference's default: int8 codes for
+    fp16 inputs, e4m3 for bf16.  Code tensors are torch.int8 or torch.float8_e4m3fn."""
+    _require_cuda(q, k, v)
+    lib = _native.load()
+    b, h, n, d = q.shape
+    if int8 is None:
+        int8 = q.dtype == torch.float16
+    n_pad, bh, dev = pad_len(n), b * h, q.device
+    code_dt = torch.int8 if int8 else torch.float8_e4m3fn
+    u8 = dict(dtype=torch.uint8, device=dev)
+    f32 = dict(dtype=torch.float32, device=dev)
+    out = dict(
+        q8=torch.empty((bh, n, d), **u8), sq=torch.empty((bh, n), **f32),
+        k8=torch.empty((bh, n_pad, d), **u8), sk=torch.empty((bh, n_pad), **f32),
+        v8t=torch.empty((bh, d, n_pad), **u8), sv=torch.empty((bh, n_pad), **f32),
+        svp=torch.empty((bh, n_pad), **f32), S=torch.empty((bh,), **f32),
+        mean=torch.empty((bh, d), **f32) if smooth_k else None)
+    ctrl = torch.empty((lib.sage_prologue_ctrl_bytes(b, h, n),), **u8)
+    with torch.cuda.device(dev):
+        rc = lib.sage_prologue(
+            _ptr(q), _ptr(k), _ptr(v), _ptr(out["q8"]), _ptr(out["sq"]), _ptr(out["k8"]),
+            _ptr(out["sk"]), _ptr(out["v8t"]), _ptr(out["sv"]), _ptr(out["svp"]), _ptr(out["S"]),
+            _ptr(out["mean"]), _ptr(ctrl), b, h, n, n_pad, _bhr(q), _bhr(k), _bhr(v),
+            _dtype_code(q.dtype), _native.SAGE_QK_INT8 if int8 else _native.SAGE_QK_E4M3,
+            1 if smooth_k else 0, _stream(dev))
+    _native.check(rc, "sage_prologue")
+    ctrl.record_stream(torch.cuda.current_stream(dev))
+    out["q8"] = out["q8"].view(code_dt)
+    out["k8"] = out["k8"].view(code_dt)
+    out["v8t"] = out["v8t"].view(torch.float8_e4m3fn)
+    out.update(n=n, n_pad=n_pad, int8=bool(int8), B=b, H=h)
+    return out
+
+
+def attn_launch(pq: Dict[str, torch.Tensor], out: torch.Tensor, is_causal: bool, sm_scale: float,
+                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Launch the attention kernel on a prologue result; `out` is a logical (B,H,N,D) view that
+    is written in place.  Returns the int32 status tensor (zero unless a bounded wait gave up)."""
+    lib = _native.load()
+    dev = out.device
+    b, h, n, n_pad = pq["B"], pq["H"], pq["n"], pq["n_pad"]
+    if status is None:
+        status = torch.zeros((1,), dtype=torch.int32, device=dev)
+    with torch.cuda.device(dev):
+        rc = lib.sage_attn_fwd(
+            _ptr(pq["q8"]), _ptr(pq["sq"]), _ptr(pq["k8"]), _ptr(pq["sk"]), _ptr(pq["v8t"]),
+            _ptr(pq["svp"]), _ptr(pq["S"]), _ptr(out), b, h, n, n_pad, _bhr(out),
+            1 if is_causal else 0, float(sm_scale), _dtype_code(out.dtype),
+            _native.SAGE_QK_INT8 if pq["int8"] else _native.SAGE_QK_E4M3, _ptr(status), _stream(dev))
+    _native.check(rc, "sage_attn_fwd")
+    return status
+
+
+# ---- the whole call ------------------------------------------------------------------------------
+_ws_lock = threading.Lock()
+_ws_cache: "OrderedDict[Tuple, torch.Tensor]" = OrderedDict()
+_WS_CACHE_ENTRIES = 4
+
+
+def _workspace(dev, stream_id: int, b: int, h: int, n: int) -> torch.Tensor:
+    """A cached workspace per (device, stream, shape): intermediates of one call live only until
+    the attention kernel of that call has run, and calls on one stream are ordered."""
+    key = (dev.index, stream_id, b, h, n)
+    with _ws_lock:
+        ws = _ws_cache.get(key)
+        if ws is not None:
+            _ws_cache.move_to_end(key)
+            return ws
+    nbytes = _native.load().sage_workspace_bytes(b, h, n)
+    ws = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
+    with _ws_lock:
+        _ws_cache[key] = ws
+        while len(_ws_cache) > _WS_CACHE_ENTRIES:
+            _ws_cache.popitem(last=False)
+    return ws
+
+
+def clear_workspaces():
+    with _ws_lock:
+        _ws_cache.clear()
+
+
+def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=True,
+              int8: Optional[bool] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Prologue + attention through the single C entry point `sage_attention`.  Returns a tensor
+    with q's shape, dtype and layout.  Raises ValueError for a call outside the envelope."""
+    reason = envelope_reason(q, k, v, tensor_layout)
+    with _counters_lock:
+        _counters["calls"] += 1
+        if reason is not None:
+            _counters["refusals"] += 1
+    if reason is not None:
+        if reason == "device" and not (q.is_cuda and k.is_cuda and v.is_cuda):
+            raise ValueError("sageattn (B200 path) needs CUDA tensors; there is no CPU path")
+        if reason == "head_dim":
+            raise NotImplementedError("sageattn (B200 path) serves head_dim 128 only")
+        raise ValueError("sageattn (B200 path) cannot serve this call: %s" % reason)
+    lib = _native.load()
+    if tensor_layout == "NHD":
+        ql, kl, vl = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
+    else:
+        ql, kl, vl = q, k, v
+    b, h, n, d = ql.shape
+    dev = q.device
+    if sm_scale is None:
+        sm_scale = d ** -0.5
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=dev)
+    ol = out.transpose(1, 2) if tensor_layout == "NHD" else out
+    if tuple(ol.shape) != (b, h, n, d) or out.dtype != q.dtype or strided_view_reason(ol) is not None:
+        raise ValueError("out must have q's shape and dtype and be a servable view")
+    if int8 is None:
+        qk_mode = -1
+    else:
+        qk_mode = _native.SAGE_QK_INT8 if int8 else _native.SAGE_QK_E4M3
+    stream = torch.cuda.current_stream(dev)
+    ws = _workspace(dev, int(stream.cuda_stream), b, h, n)
+    with torch.cuda.device(dev):
+        rc = lib.sage_attention(
+            _ptr(ql), _ptr(kl), _ptr(vl), _ptr(ol), _ptr(ws), ws.numel(), b, h, n,
+            _bhr(ql), _bhr(kl), _bhr(vl), _bhr(ol), _dtype_code(q.dtype), qk_mode,
+            1 if is_causal else 0, 1 if smooth_k else 0, float(sm_scale),
+            ctypes.c_void_p(int(stream.cuda_stream)))
+    _native.check(rc, "sage_attention")
+    return out
+
+
+def workspace_views(b: int, h: int, n: int, ws: torch.Tensor, int8: bool) -> Dict[str, torch.Tensor]:
+    """Typed views of the intermediates inside a `sage_attention` workspace (for tests/tools)."""
+    lib = _native.load()
+    offs = (ctypes.c_size_t * 11)()
+    if lib.sage_workspace_layout(b, h, n, offs) != 11:
+        raise _native.SageNativeError("sage_workspace_layout failed")
+    bh, n_pad, d = b * h, pad_len(n), HEAD_DIM
+    code_dt = torch.int8 if int8 else torch.float8_e4m3fn
+
+    def seg(i, nbytes):
+        return ws[offs[i]: offs[i] + nbytes]
+    return dict(
+        q8=seg(0, bh * n * d).view(code_dt).view(bh, n, d),
+        sq=seg(1, bh * n * 4).view(torch.float32).view(bh, n),
+        k8=seg(2, bh * n_pad * d).view(code_dt).view(bh, n_pad, d),
+        sk=seg(3, bh * n_pad * 4).view(torch.float32).view(bh, n_pad),
+        v8t=seg(4, bh * n_pad * d).view(torch.float8_e4m3fn).view(bh, d, n_pad),
+        sv=seg(5, bh * n_pad * 4).view(torch.float32).view(bh, n_pad),
+        svp=seg(6, bh * n_pad * 4).view(torch.float32).view(bh, n_pad),
+        S=seg(7, bh * 4).view(torch.float32),
+        mean=seg(8, bh * d * 4).view(torch.float32).view(bh, d),
+        status=seg(10, 4).view(torch.int32))
+
+
+def last_status(q_like: torch.Tensor, b: int, h: int, n: int) -> int:
+    """Status word of the most recent call of that shape on the current stream (synchronises)."""
+    dev = q_like.device
+    ws = _workspace(dev, int(torch.cuda.current_stream(dev).cuda_stream), b, h, n)
+    return int(workspace_views(b, h, n, ws, True)["status"].item())
+
+
+def status() -> dict:
+    """Small status record in the spirit of the reference's int8_status()/bf16_status()
+    (sageattention/sk1_backend/__init__.py:529-558)."""
+    info = dict(library=_native.LIB_PATH, loaded=_native._lib is not None, calls=_counters["calls"],
+                refusals=_counters["refusals"], arch="sm_100a", tile=TILE, head_dim=HEAD_DIM)
+    try:
+        info["version"] = _native.load().sage_version()
+    except _native.SageNativeError as exc:
+        info["error"] = str(exc)
+    return info

@@ -1,0 +1,112 @@
+"""Host-side contract of the drop-in package: signatures, acceptance rule, refusals (CPU only)."""
+import inspect
+
+import pytest
+import torch
+
+import sageattention
+from sageattention import b200_backend as be
+
+
+def _t(*shape, dtype=torch.float16):
+    return torch.zeros(*shape, dtype=dtype)
+
+
+def test_public_names_and_signature():
+    for name in ("sageattn", "sageattn_qk_int8_pv_fp8", "sageattn_qk_int8_pv_fp8_cuda",
+                 "sageattn_qk_int8_pv_fp8_cuda_sm90"):
+        assert callable(getattr(sageattention, name))
+    sig = inspect.signature(sageattention.sageattn)
+    names = list(sig.parameters)
+    assert names[:10] == ["q", "k", "v", "tensor_layout", "is_causal", "sm_scale", "return_lse",
+                          "sk1_backend", "sk1_int8", "sk1_bf16"]
+    # callers probe for an attn_mask parameter; there must be none
+    assert "attn_mask" not in sig.parameters
+    assert sig.parameters["tensor_layout"].default == "HND"
+    assert sig.parameters["is_causal"].default is False
+    up = inspect.signature(sageattention.sageattn_qk_int8_pv_fp8)
+    assert up.parameters["smooth_k"].default is True
+    assert up.parameters["qk_quant_gran"].default == "per_thread"
+    assert up.parameters["pv_accum_dtype"].default == "fp32+fp16"
+
+
+def test_attn_mask_lse_smooth_v_are_refused():
+    q = _t(1, 1, 4, 128)
+    with pytest.raises(NotImplementedError):
+        sageattention.sageattn(q, q, q, attn_mask=torch.ones(4, 4))
+    with pytest.raises(NotImplementedError):
+        sageattention.sageattn(q, q, q, return_lse=True)
+    with pytest.raises(NotImplementedError):
+        sageattention.sageattn(q, q, q, smooth_v=True)
+    with pytest.raises(NotImplementedError):
+        sageattention.sageattn(q, q, q, sk1_backend=False)
+    with pytest.raises(ValueError):
+        sageattention.sageattn_qk_int8_pv_fp8(q, q, q, qk_quant_gran="per_block")
+
+
+def test_cpu_tensors_raise_no_fallback():
+    q = _t(1, 1, 4, 128)
+    with pytest.raises(ValueError, match="no CPU path"):
+        sageattention.sageattn(q, q, q)
+
+
+def test_strided_view_reasons_in_order():
+    ok = _t(2, 3, 16, 128)
+    assert be.strided_view_reason(ok) is None
+    assert be.strided_view_reason(_t(3, 16, 128)) == "rank"
+    assert be.strided_view_reason(ok.transpose(2, 3)) == "stride_last"
+    assert be.strided_view_reason(_t(1, 1, 16, 128).expand(2, 3, 16, 128)) == "stride_nonpos"
+    odd = torch.zeros(2 * 3 * 16 * 132, dtype=torch.float16).as_strided((2, 3, 16, 128), (3 * 16 * 132, 16 * 132, 132, 1))
+    assert be.strided_view_reason(odd) == "stride_align"
+    off = torch.zeros(2 * 3 * 16 * 128 + 8, dtype=torch.float16)[4:].as_strided((2, 3, 16, 128), (3 * 16 * 128, 16 * 128, 128, 1))
+    assert be.strided_view_reason(off) == "ptr_align"
+    overlap = torch.zeros(4096, dtype=torch.float16).as_strided((1, 2, 16, 128), (4096, 64 * 8, 128, 1))
+    assert be.strided_view_reason(overlap) == "stride_overlap"
+
+
+def test_accepted_views():
+    # physical NHD read as HND, and a fused-QKV view whose row stride is 3*H*D
+    nhd = _t(2, 16, 3, 128).transpose(1, 2)
+    assert be.strided_view_reason(nhd) is None
+    fused = _t(2, 16, 3, 3 * 128)
+    qv = fused[..., :128].transpose(1, 2)
+    assert be.strided_view_reason(qv) is None
+    # unsqueeze(0) gives B=1 a small batch stride; size-1 dims are ignored by the overlap rule
+    one = _t(3, 16, 128).unsqueeze(0)
+    assert be.strided_view_reason(one) is None
+
+
+@pytest.mark.parametrize("mutate,reason", [
+    (lambda q, k, v: (q, k, v.float()), "dtype"),
+    (lambda q, k, v: (q.float(), k.float(), v.float()), "dtype"),
+    (lambda q, k, v: (q[..., :64], k[..., :64], v[..., :64]), "stride_align"),
+    (lambda q, k, v: (q, k[:, :, :8], v[:, :, :8]), "seq_len"),
+    (lambda q, k, v: (q, k[:, :1], v[:, :1]), "heads"),
+    (lambda q, k, v: (q, k[:1], v[:1]), "batch"),
+])
+def test_envelope_reasons(mutate, reason):
+    q, k, v = _t(2, 2, 16, 128), _t(2, 2, 16, 128), _t(2, 2, 16, 128)
+    q, k, v = mutate(q, k, v)
+    got = be.envelope_reason(q, k, v, "HND", require_cuda=False)
+    if reason == "stride_align":
+        # a D=64 slice of a D=128 tensor keeps a 128-element row stride: it passes the stride rule
+        # and is refused for its head_dim
+        assert got == "head_dim"
+    else:
+        assert got == reason
+
+
+def test_envelope_layout_and_flags():
+    q = _t(1, 1, 4, 128)
+    assert be.envelope_reason(q, q, q, "HDN", require_cuda=False) == "layout"
+    assert be.envelope_reason(q, q, q, "HND", return_lse=True, require_cuda=False) == "return_lse"
+    assert be.envelope_reason(q, q, q, "HND", smooth_v=True, require_cuda=False) == "smooth_v"
+    assert be.envelope_reason(q, q, q, "HND", attn_mask=q, require_cuda=False) == "attn_mask"
+    assert be.envelope_reason(q, q, q, "HND", require_cuda=True) == "device"
+    assert be.envelope_reason(q, q, q, "NHD", require_cuda=False) is None
+    d64 = _t(1, 1, 4, 64)
+    assert be.envelope_reason(d64, d64, d64, "HND", require_cuda=False) == "head_dim"
+
+
+def test_pad_len():
+    assert [be.pad_len(n) for n in (1, 127, 128, 129, 8771, 47520)] == [128, 128, 128, 256, 8832, 47616]
