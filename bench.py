@@ -1,0 +1,319 @@
+"""Benchmark of the quantize-then-attend call on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--causal]
+
+One step = one full `sageattn` call (quantisation prologue + attention kernel) on the video-length
+configuration the headline metric is quoted on: B=1, H=48, N=47520, D=128, fp16, smooth_k on,
+Q, K, V ~ N(0,1) with a seeded 0.1 % of the K tokens scaled x50 (seeded synthetic data stands in
+for the reference's activation captures).  With N > 1 GPUs (launched with torch.distributed.run,
+one rank per GPU) every rank runs that workload on its own batch element: the path shards over
+(batch, head) with no collective, so the per-GPU work is fixed and the scaling is "weak".
+
+Printed: ONE JSON line with whole-job TFLOPS (4*B*H*N^2*D flops per call, halved when causal),
+the attention kernel's tensor roofline, the prologue's HBM figure, an end-to-end number measured
+through the public API from pinned host buffers, and a bounded CPU baseline (the oracle, i.e. a
+PyTorch port of the reference's numerics, on the host cores).
+
+`--impl reference` times that CPU port alone, with all host threads, on a bounded sample of the
+same workload (the reference's own kernels are AMD gfx1201 binaries and cannot run here).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "sageattention-rdna4_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+B, H, N, D = 1, 48, 47520, 128
+SEED = 0
+METRIC = "attention TFLOPS (full call incl. quant) at H=48 N=47520 D=128"
+# DRAM bytes of one attention-kernel launch at this workload, from the ncu capture summarised in
+# profiles/ (set to None until a capture of the current kernel exists).
+ATTN_DRAM_TRAFFIC_BYTES = None
+
+
+def flops(causal: bool, batch: int = B) -> float:
+    return 4.0 * batch * H * N * N * D * (0.5 if causal else 1.0)
+
+
+def prologue_bytes() -> float:
+    """Minimum traffic of the prologue: read Q, K, V once; write the three code tensors and the
+    scales (K read once; the second read for the mean is not counted)."""
+    bh, n_pad = B * H, (N + 127) // 128 * 128
+    return 3 * bh * N * D * 2 + bh * N * D + 2 * bh * n_pad * D + 4 * (bh * N + 3 * bh * n_pad)
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            m = json.load(f)
+        return dict(source="measured", hbm_gbs=float(m["hbm_gbs"]), bf16_tflops=float(m["bf16_tflops"]),
+                    bf16_tflops_sustained=float(m.get("bf16_tflops_sustained", m["bf16_tflops"])))
+    return dict(source="fallback", hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML (read-only) during the timed region."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            nv.nvmlClocksThrottleReasonHwSlowdown: "hw_slowdown",
+            nv.nvmlClocksThrottleReasonHwThermalSlowdown: "hw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwThermalSlowdown: "sw_thermal_slowdown",
+            nv.nvmlClocksThrottleReasonSwPowerCap: "sw_power_cap",
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h)
+                for bit, name in names.items():
+                    if mask & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.05)
+
+    def __enter__(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self) -> dict:
+        med = statistics.median(self.samples) if self.samples else None
+        return dict(sm_mhz=med, sm_max_mhz=self.max_mhz, reasons=sorted(self.reasons), samples=len(self.samples))
+
+
+def physical_gpu_index(local: int) -> int:
+    vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+    if vis:
+        try:
+            return int(vis.split(",")[local])
+        except (ValueError, IndexError):
+            return local
+    return local
+
+
+def make_workload(dtype=torch.float16):
+    from oracle import ref_numerics as R   # input generator only; nothing of the oracle is timed here
+    return R.make_inputs(B, H, N, D, dtype, seed=SEED, outlier_frac=0.001)
+
+
+def cpu_baseline(causal: bool, rows: int = 0) -> dict:
+    """The oracle (PyTorch port of the reference numerics) on the host cores, on a bounded sample:
+    the full prologue of ONE of the 48 heads plus the attention of `rows` query rows of that head
+    (the first rows against all keys; when causal, the block in the middle of the sequence, which
+    sees the average number of keys).  Same flop formula as the GPU number."""
+    from oracle import ref_numerics as R
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    rows = rows or N
+    q, k, v = R.make_inputs(1, 1, N, D, torch.float16, seed=SEED, outlier_frac=0.001)
+    row0 = max(0, N // 2 - rows // 2) if causal else 0
+    t0 = time.perf_counter()
+    pq = R.prologue(q, k, v, smooth_k=True)
+    R.attend(pq["q8"][:, :, row0:row0 + rows], pq["sq"][:, :, row0:row0 + rows], pq["k8"], pq["sk"], pq["v8"],
+             pq["svp"], pq["S"], N, causal, D ** -0.5, torch.float16, row_chunk=2048, row0=row0)
+    dt = time.perf_counter() - t0
+    keys = (row0 + rows / 2.0) if causal else N
+    fl = 4.0 * rows * keys * D
+    return dict(value=fl / dt / 1e12, unit="TFLOP/s", cores=cores, kind="port",
+                sample="1 of %d heads: prologue of that head + attention of %d query rows (from row %d) over "
+                       "%d keys = %.2e of the call's flops, %.1f s" % (H, rows, row0, int(keys), fl / flops(causal), dt))
+
+
+def run_reference(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    times = []
+    base = None
+    for i in range(args.warmup + args.steps):
+        base = cpu_baseline(args.causal)
+        if i >= args.warmup:
+            times.append(base["value"])
+    val = statistics.median(times)
+    base["value"] = val
+    line = dict(metric=METRIC, value=val, unit="TFLOP/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+                ms_per_step=None, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="int8+fp8",
+                data="synthetic", impl="reference",
+                config=workload_config(args.causal, args.gpus), cpu_baseline=base,
+                e2e=dict(value=val, unit="TFLOP/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
+    print(json.dumps(line))
+    return 0
+
+
+def workload_config(causal: bool, gpus: int) -> dict:
+    return dict(workload="video-length attention B=%d(per GPU) H=%d N=%d D=%d fp16 %s smooth_k, 0.1%% K tokens x50"
+                % (B, H, N, D, "causal" if causal else "non-causal"),
+                global_batch=B * gpus, heads=H, seq_len=N, head_dim=D, causal=causal, seed=SEED,
+                sharding="batch x head units across GPUs, no collective" if gpus > 1 else "single GPU",
+                l2="inputs (3 x 584 MB) exceed the 126 MB L2; no explicit flush")
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--causal", action="store_true")
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--shape", default=None, metavar="H,N",
+                    help="override heads and sequence length (profiling captures on a smaller case)")
+    args = ap.parse_args()
+    if args.shape:
+        global H, N
+        H, N = (int(x) for x in args.shape.split(","))
+    args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
+    if args.impl == "reference":
+        return run_reference(args)
+
+    import torch.distributed as dist
+    import sageattention
+    from sageattention import b200_backend as be
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device: the product has no CPU path")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    causal = args.causal
+    q_h, k_h, v_h = (t.pin_memory() for t in make_workload())
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    out_h = torch.empty_like(q_h).pin_memory()
+    stream = torch.cuda.current_stream(dev)
+
+    def sync_all():
+        torch.cuda.synchronize(dev)
+        if world > 1:
+            dist.barrier()
+            torch.cuda.synchronize(dev)
+
+    def max_over_ranks(ms: float) -> float:
+        if world == 1:
+            return ms
+        t = torch.tensor([ms], dtype=torch.float64, device=dev)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    # ---- device-resident throughput through the public API ----
+    for _ in range(args.warmup):
+        out = sageattention.sageattn(q, k, v, is_causal=causal)
+    sync_all()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with ClockSampler(physical_gpu_index(local)) as clk:
+        e0.record(stream)
+        for _ in range(args.steps):
+            out = sageattention.sageattn(q, k, v, is_causal=causal)
+        e1.record(stream)
+        sync_all()
+    ms_total = max_over_ranks(e0.elapsed_time(e1))
+    ms_step = ms_total / args.steps
+    value = flops(causal, B * world) / (ms_step * 1e-3) / 1e12
+    status = be.last_status(q, B, H, N)
+
+    # ---- per-kernel durations (same launches through the two reference-shaped entry points) ----
+    pq = be.quant_qkv(q, k, v)
+    o2 = torch.empty_like(q)
+    st = torch.zeros(1, dtype=torch.int32, device=dev)
+    ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    pro_ms, att_ms = [], []
+    for i in range(args.warmup + args.steps):
+        ev[0].record(stream)
+        pq = be.quant_qkv(q, k, v)
+        ev[1].record(stream)
+        be.attn_launch(pq, o2, causal, D ** -0.5, status=st)
+        ev[2].record(stream)
+        torch.cuda.synchronize(dev)
+        if i >= args.warmup:
+            pro_ms.append(ev[0].elapsed_time(ev[1]))
+            att_ms.append(ev[1].elapsed_time(ev[2]))
+    att = statistics.mean(att_ms)
+    pro = statistics.mean(pro_ms)
+    pk = peaks()
+    peak8 = 2.0 * pk["bf16_tflops_sustained"]
+    achieved = flops(causal) / (att * 1e-3) / 1e12
+    roofline = dict(bound="tensor", kernel="attn_fwd_kernel", achieved=achieved, peak=peak8, unit="TFLOP/s",
+                    frac=achieved / peak8, traffic=ATTN_DRAM_TRAFFIC_BYTES, ms_per_launch=att,
+                    peak_basis="2 x bf16_tflops_sustained (%s) of MEASURED_PEAKS.json: dense 8-bit rate is twice bf16; "
+                               "vs 2 x burst %.0f: %.3f; vs nominal 4500: %.3f"
+                               % (pk["source"], 2 * pk["bf16_tflops"], achieved / (2 * pk["bf16_tflops"]), achieved / 4500.0))
+    pro_gbs = prologue_bytes() / (pro * 1e-3) / 1e9
+    prologue = dict(bound="hbm", kernel="kmean_kernel + quant_qkv_kernel", achieved=pro_gbs, peak=pk["hbm_gbs"],
+                    unit="GB/s", frac=pro_gbs / pk["hbm_gbs"], ms=pro, algorithmic_bytes=prologue_bytes())
+
+    # ---- end to end from pinned host buffers through the public API ----
+    def e2e_step():
+        qd = q_h.to(dev, non_blocking=True)
+        kd = k_h.to(dev, non_blocking=True)
+        vd = v_h.to(dev, non_blocking=True)
+        o = sageattention.sageattn(qd, kd, vd, is_causal=causal)
+        out_h.copy_(o, non_blocking=True)
+
+    for _ in range(2):
+        e2e_step()
+    sync_all()
+    e0.record(stream)
+    for _ in range(args.steps):
+        e2e_step()
+    e1.record(stream)
+    sync_all()
+    e2e_ms = max_over_ranks(e0.elapsed_time(e1)) / args.steps
+    nbytes = q_h.numel() * q_h.element_size()
+    e2e = dict(value=flops(causal, B * world) / (e2e_ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=e2e_ms,
+               h2d_bytes_per_step=3 * nbytes, d2h_bytes_per_step=nbytes)
+
+    if world > 1:
+        dist.barrier()
+    if rank == 0:
+        line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None,
+                    dtype="int8+fp8", data="synthetic", config=workload_config(causal, world),
+                    roofline=roofline, prologue=prologue, e2e=e2e, gpu_launches=3 * args.steps,
+                    clocks=clk.summary(), kernel_status=status)
+        if not args.no_cpu_baseline and world == 1:
+            line["cpu_baseline"] = cpu_baseline(causal)
+        print(json.dumps(line))
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

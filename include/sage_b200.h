@@ -95,6 +95,11 @@ int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* 
                   int causal, float sm_scale, int out_dtype, int qk_mode,
                   int32_t* status, void* stream);
 
+/* Debugging aid (process-global, not thread-safe): while `ptr` is non-null every later attention
+ * launch copies the raw Q.K^T accumulators (int32, or fp32 bits for e4m3 codes) of key tile
+ * `key_tile` to ptr[((bh * q_tiles + q_tile) * 128 + row) * 128 + key].  Pass NULL to stop. */
+void sage_debug_score_dump(void* ptr, int key_tile);
+
 /* Bytes of workspace `sage_attention` needs for one call (all intermediates + ctrl + status). */
 size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N);
 

@@ -163,11 +163,12 @@ def row_score_scale(sq: torch.Tensor, sm_scale: float) -> torch.Tensor:
 def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tensor,
            v8: torch.Tensor, svp: torch.Tensor, s_fold: torch.Tensor, n: int, causal: bool,
            sm_scale: float, out_dtype: torch.dtype, tile: int = REF_BN,
-           row_chunk: int = 2048) -> torch.Tensor:
+           row_chunk: int = 2048, row0: int = 0) -> torch.Tensor:
     """The attention loop of sk1_t6i.hip:151-299 on already-quantised operands.
 
-    q8 (B,H,N,D), sq (B,H,N); k8, v8 (B,H,n_pad,D) with n_pad a multiple of `tile`; sk, svp
-    (B,H,n_pad) where svp = SV / S; s_fold (B,H).  Per query row, tiles of `tile` keys in
+    q8 (B,H,R,D), sq (B,H,R) hold the query rows row0 .. row0+R-1 (all N rows by default); k8, v8
+    (B,H,n_pad,D) with n_pad a multiple of `tile`; sk, svp (B,H,n_pad) where svp = SV / S;
+    s_fold (B,H); `n` is the number of live keys.  Per query row, tiles of `tile` keys in
     increasing order: integer (or fp32 for e4m3 codes) dot products, s = f32(t) * f32(c_q * sk),
     mask, one running-max update per tile, p = exp2(s - m), l = l*alpha + sum(p) taken BEFORE
     the fold, p8 = e4m3(p * f32(svp*448)), acc = acc*alpha + p8 @ v8 in fp32; epilogue
@@ -178,25 +179,25 @@ def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tenso
     try:
         b, h, nq, d = q8.shape
         n_pad = k8.shape[2]
-        assert n_pad % tile == 0 and nq == n
+        assert n_pad % tile == 0 and row0 + nq <= n
         dev = q8.device
         kf = k8.float()
         vf = v8.float()
         stage = stage_sv(svp)
         cq_all = row_score_scale(sq, sm_scale)
-        out = torch.empty(b, h, n, d, dtype=out_dtype, device=dev)
+        out = torch.empty(b, h, nq, d, dtype=out_dtype, device=dev)
         neg_inf = _f32(float("-inf"), dev)
-        for r0 in range(0, n, row_chunk):
-            r1 = min(n, r0 + row_chunk)
+        for r0 in range(0, nq, row_chunk):
+            r1 = min(nq, r0 + row_chunk)
             qf = q8[:, :, r0:r1].float()
             cq = cq_all[:, :, r0:r1]
-            rows = torch.arange(r0, r1, device=dev)
+            rows = torch.arange(row0 + r0, row0 + r1, device=dev)
             m = torch.full((b, h, r1 - r0), float("-inf"), dtype=torch.float32, device=dev)
             l = torch.zeros(b, h, r1 - r0, dtype=torch.float32, device=dev)
             acc = torch.zeros(b, h, r1 - r0, d, dtype=torch.float32, device=dev)
             # the reference visits tiles j < min(n_tiles, 2c+2) for the CTA owning 128 queries
             # (sk1_t6i.hip:88); tiles past the last query of the chunk are fully masked anyway
-            last_key = (r1 - 1) if causal else (n - 1)
+            last_key = (row0 + r1 - 1) if causal else (n - 1)
             for j in range(0, last_key // tile + 1):
                 c0, c1 = j * tile, (j + 1) * tile
                 t = torch.matmul(qf, kf[:, :, c0:c1].transpose(2, 3))

@@ -186,6 +186,8 @@ struct AttnKArgs {
   long long o_sb, o_sh, o_sr;
   float sm_scale;
   int32_t* status;
+  uint32_t* dbg;      // when non-null: raw score accumulators of key tile `dbg_tile` are copied here
+  int dbg_tile;
 };
 
 template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -328,6 +330,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_SFREE));
+        if (a.dbg != nullptr && j == a.dbg_tile) {
+          uint32_t* d = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + row) * TILE;
+#pragma unroll
+          for (int k = 0; k < TILE; ++k) d[k] = acc[k];
+        }
 
         const float4* skv = reinterpret_cast<const float4*>(gbase + OFF_SK + s * VEC_BYTES);
         const float4* svv = reinterpret_cast<const float4*>(gbase + OFF_SV + s * VEC_BYTES);
@@ -488,6 +495,10 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t r
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+static uint32_t* g_dbg_ptr = nullptr;
+static int g_dbg_tile = 0;
+void set_score_dump(void* ptr, int tile) { g_dbg_ptr = reinterpret_cast<uint32_t*>(ptr); g_dbg_tile = tile; }
+
 template <bool INT8, bool CAUSAL, typename OutT>
 static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                                const AttnKArgs& ka, dim3 grid, cudaStream_t st) {
@@ -512,6 +523,7 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   ka.N = p.N; ka.N_pad = p.N_pad; ka.H = p.H;
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
+  ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;
   dim3 grid((unsigned)((p.N + TILE - 1) / TILE), (unsigned)bh);
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
   cudaError_t e;

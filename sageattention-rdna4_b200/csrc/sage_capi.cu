@@ -139,6 +139,8 @@ int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* 
   return SAGE_OK;
 }
 
+void sage_debug_score_dump(void* ptr, int key_tile) { sage::set_score_dump(ptr, key_tile); }
+
 size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N) {
   if (B < 1 || H < 1 || N < 1) return 0;
   return carve(B, H, N).total;

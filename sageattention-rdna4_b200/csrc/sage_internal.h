@@ -37,4 +37,7 @@ size_t prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
 // Returns cudaSuccess or an error; `why` (if non-null) receives a static description on failure.
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why);
 
+// Debug aid: subsequent attention launches copy the raw score accumulators of one key tile.
+void set_score_dump(void* ptr, int tile);
+
 }  // namespace sage
