@@ -150,16 +150,25 @@ def test_image_size_config(dtype, causal):
 
 def test_video_length_properties():
     """B=1,H=2 at N=47520 (two of the 48 heads; every head is independent) with 0.1 % of the K
-    tokens scaled x50: finite output, rows sum-normalised (V = const gives that const back), and
-    the sampled rows agree with exact attention."""
+    tokens scaled x50, causal.  The oracle is the same restatement evaluated by torch on the
+    device.  Head 1 has a constant V: its output must equal the oracle's, which is NOT the
+    constant for every row -- when an outlier key dominates a row, the many small probabilities
+    fall below e4m3's smallest subnormal after the fold and drop out of P.V while they stay in the
+    row sum; that is a property of the reference's numerics, reproduced here."""
     n = 47520
     q, k, v = R.make_inputs(1, 2, n, seed=0, outlier_frac=0.001, device="cuda")
     v[:, 1] = 0.75
     out = _run(q, k, v, True)
     assert torch.isfinite(out.float()).all()
-    assert (out[:, 1].float() - 0.75).abs().max().item() < 0.02
+    o128 = R.sageattn_oracle(q, k, v, is_causal=True, tile=128)
+    o64 = R.sageattn_oracle(q, k, v, is_causal=True, tile=64)
+    assert R.cosine(out, o128) >= COS_SAME and R.rel_l1(out, o128) <= L1_SAME
+    assert R.cosine(out, o64) >= COS_REF and R.rel_l1(out, o64) <= L1_REF
+    assert (out[:, 1].float() - o128[:, 1].float()).abs().max().item() < 0.05
+    assert out[:, 1].float().max().item() <= 0.7505          # never above the constant
     rows = torch.tensor([0, 1, 127, 128, 5000, 23760, 47519], device="cuda")
     s = torch.matmul(q[0, 0, rows].float(), k[0, 0].float().t()) * 128 ** -0.5
     s = s.masked_fill(torch.arange(n, device="cuda")[None, :] > rows[:, None], float("-inf"))
     ref = torch.matmul(torch.softmax(s, -1), v[0, 0].float())
-    assert R.rel_rms(out[0, 0, rows], ref) < MAX_REL_RMS
+    e_gpu, e_ora = R.rel_rms(out[0, 0, rows], ref), R.rel_rms(o64[0, 0, rows], ref)
+    assert e_gpu <= 1.1 * e_ora + 1e-3

@@ -13,7 +13,7 @@ pytestmark = pytest.mark.gpu
 def _check_against(pq_gpu, pq_ref, n, smooth):
     bh = pq_gpu["B"] * pq_gpu["H"]
     n_pad = pq_gpu["n_pad"]
-    flat = lambda t: t.reshape(bh, *t.shape[2:])
+    flat = lambda t: t.reshape(bh, *t.shape[2:]).cpu()
     assert bytes_equal(pq_gpu["q8"], flat(pq_ref["q8"])), "q8"
     assert torch.equal(pq_gpu["sq"].cpu(), flat(pq_ref["sq"])), "sq"
     assert bytes_equal(pq_gpu["k8"], flat(pq_ref["k8"])), "k8"
