@@ -1,20 +1,25 @@
 // Quantised flash attention for B200 (sm_100a): tcgen05 tensor cores, TMEM accumulators, TMA tiles.
 //
 // One CTA owns 128 queries of one (batch, head) and streams 128-key tiles; two CTAs share an SM so
-// that one CTA's softmax overlaps the other's matrix products.  Roles inside a CTA (192 threads):
+// that one CTA's softmax overlaps the other's matrix products.  Roles inside a CTA (320 threads):
 //   warp 0     TMA producer: Q tile once, then a 2-deep ring of K tiles and a 2-deep ring of
 //              V^T tiles, each V stage carrying that tile's 128 K scales and 128 staged V factors
 //   warp 1     allocates 256 TMEM columns; one thread issues every tcgen05.mma
-//   warps 2-5  softmax: thread r owns query row r of the tile (TMEM lane r)
+//   warps 2-9  softmax: two threads per query row (TMEM lane = row); warps 2-5 take key columns
+//              0..63 of the tile, warps 6-9 columns 64..127; a pair exchanges its row maximum
+//              through shared memory and a two-arrival mbarrier
 // Per key tile j:
 //   S  = Q8 . K8^T          kind::i8 (s32) or kind::f8f6f4 (f32), M=N=K=128, into TMEM cols 0..127
-//   s  = f32(S) * (c_q * sk[key])   (log2 domain), mask, row max, alpha = exp2(m_old - m_new)
-//   O *= alpha in TMEM when some row's max moved; l = l*alpha + sum(p), p = exp2(s - m)
-//   P8 = e4m3(p * svp[key]) written to shared memory in the 128-byte swizzled K-major layout
+//   u  = f32(S) * sk[key]; mask; row max m (in the u domain); s = c_q * u is the log2-domain score
+//   alpha = exp2(c_q*(m_old - m_new)); O *= alpha in TMEM when some row's max moved
+//   p  = exp2(c_q*u - c_q*m); l = l*alpha + sum(p); P8 = e4m3(p * svp[key]) written to shared
+//        memory in the 128-byte swizzled K-major layout
 //   O += P8 . V8            kind::f8f6f4 into TMEM cols 128..255
 // Epilogue: out = O * (S_fold / (l * 448)) -> fp16 / bf16.
 // (numerics: kernels/hip/sk1_t6i.hip:151-299 and kernels/hip/sk1_t4a1sb.hip:176-189 of the
-// reference, with a 128-key instead of a 64-key tile for the running max)
+// reference, with a 128-key instead of a 64-key tile for the running max; the two score factors
+// c_q and sk are applied one after the other instead of as one pre-multiplied factor, a
+// difference of one rounding in a quantity the reference does not pin bit-wise)
 //
 // Every wait on an mbarrier is bounded: after about two seconds, or as soon as another CTA has
 // reported a failure, the waiter records a code in the status word, the CTA drains and frees its
@@ -26,7 +31,7 @@
 
 namespace sage {
 
-constexpr int ATT_THREADS = 192;
+constexpr int ATT_THREADS = 320;
 constexpr uint32_t TILE_BYTES = TILE * HD;          // 16 KiB: 128 rows x 128 one-byte codes
 constexpr uint32_t VEC_BYTES = TILE * 4;            // 128 floats
 constexpr uint32_t OFF_Q = 0;
@@ -35,15 +40,16 @@ constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;  // 2 stages
 constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;
 constexpr uint32_t OFF_SK = OFF_P + TILE_BYTES;     // 2 stages of K scales
 constexpr uint32_t OFF_SV = OFF_SK + 2 * VEC_BYTES; // 2 stages of staged V factors
-constexpr uint32_t OFF_BAR = OFF_SV + 2 * VEC_BYTES;
-constexpr uint32_t OFF_MISC = OFF_BAR + 128;
+constexpr uint32_t OFF_XCH = OFF_SV + 2 * VEC_BYTES;// [parity][half][row] floats exchanged by a row's two threads
+constexpr uint32_t OFF_BAR = OFF_XCH + 4 * VEC_BYTES;
+constexpr uint32_t OFF_MISC = OFF_BAR + 192;
 constexpr uint32_t SMEM_USED = OFF_MISC + 64;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;   // slack for the 1024-byte alignment
 constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t TMEM_O = 128;
 
 enum Bar { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SFREE = 10,
-           BAR_PF = 11, BAR_PV = 12, BAR_COUNT = 13 };
+           BAR_PF = 11, BAR_PV = 12, BAR_X = 13 /* 4: one per TMEM lane quarter */, BAR_COUNT = 17 };
 
 enum { ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_SOFTMAX = 4 };
 
@@ -160,12 +166,29 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
         "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
         "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(taddr) : "memory");
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float y;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(y) : "f"(a), "f"(b), "f"(c));
   return y;
 }
 
@@ -201,7 +224,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 }
 
 // ------------------------------------------------------------------------------------------------
-// The kernel.  grid (ceil(N/128), B*H), block 192, two CTAs per SM.
+// The kernel.  grid (ceil(N/128), B*H), block 320, two CTAs per SM.
 // ------------------------------------------------------------------------------------------------
 template <bool INT8, bool CAUSAL, typename OutT>
 __global__ void __launch_bounds__(ATT_THREADS, 2)
@@ -230,9 +253,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar(BAR_VE + s), 1);
     }
     mbar_init(bar(BAR_SF), 1);
-    mbar_init(bar(BAR_SFREE), 4);
-    mbar_init(bar(BAR_PF), 4);
+    mbar_init(bar(BAR_SFREE), 8);
+    mbar_init(bar(BAR_PF), 8);
     mbar_init(bar(BAR_PV), 1);
+    for (int q = 0; q < 4; ++q) mbar_init(bar(BAR_X + q), 2);
     misc[1] = (*reinterpret_cast<volatile int32_t*>(a.status) != 0) ? 1u : 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -306,15 +330,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     } else {
       // ------------------------------- softmax warps ------------------------------
-      const int row = 32 * (warp & 3) + lane;               // TMEM lane == query row of the tile
+      const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
+      const int half = (warp - 2) >> 2;                     // which 64 key columns of the tile
+      const int row = 32 * quarter + lane;                  // TMEM lane == query row of the tile
       const long long q_row = (long long)q_tile * TILE + row;
-      const uint32_t t_lane = tmem + ((uint32_t)(32 * (warp & 3)) << 16);
+      const uint32_t t_s = tmem + ((uint32_t)(32 * quarter) << 16) + 64 * half;
+      const uint32_t t_o = t_s + TMEM_O;
+      // c_q = f32(f32(sm_scale * log2e) * sq); rows past N get 1 (their scores are all zero)
       const float cq = (q_row < a.N)
-          ? __fmul_rn(__fmul_rn(a.sm_scale, LOG2E_F), __ldg(a.sq + (size_t)bh * a.N + q_row)) : 0.f;
+          ? __fmul_rn(__fmul_rn(a.sm_scale, LOG2E_F), __ldg(a.sq + (size_t)bh * a.N + q_row)) : 1.f;
+      const float2 cq2 = make_float2(cq, cq);
       float m = -INFINITY, l = 0.f;
       bool ok = true;
       uint8_t* p_row = gbase + OFF_P + row * 128;
       const int swz = row & 7;
+      float* xch = reinterpret_cast<float*>(gbase + OFF_XCH);      // [parity][half][row]
+      const uint32_t xbar = bar(BAR_X + quarter);
 
       for (int j = 0; j < n_tiles; ++j) {
         const int s = j & 1;
@@ -323,52 +354,78 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        uint32_t acc[TILE];
-#pragma unroll
-        for (int i = 0; i < 4; ++i) tmem_ld32(t_lane + 32 * i, acc + 32 * i);
+        uint32_t acc[64];
+        tmem_ld32(t_s, acc);
+        tmem_ld32(t_s + 32, acc + 32);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(bar(BAR_SFREE));
         if (a.dbg != nullptr && j == a.dbg_tile) {
-          uint32_t* d = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + row) * TILE;
+          uint32_t* d = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + row) * TILE + 64 * half;
 #pragma unroll
-          for (int k = 0; k < TILE; ++k) d[k] = acc[k];
+          for (int k = 0; k < 64; ++k) d[k] = acc[k];
         }
 
-        const float4* skv = reinterpret_cast<const float4*>(gbase + OFF_SK + s * VEC_BYTES);
-        const float4* svv = reinterpret_cast<const float4*>(gbase + OFF_SV + s * VEC_BYTES);
-        float sc[TILE];
+        const float4* skv = reinterpret_cast<const float4*>(gbase + OFF_SK + s * VEC_BYTES) + 16 * half;
+        const float4* svv = reinterpret_cast<const float4*>(gbase + OFF_SV + s * VEC_BYTES) + 16 * half;
+        float2 u[32];                                       // u[i] = scores of keys 2i, 2i+1 (times sk)
 #pragma unroll
-        for (int k4 = 0; k4 < TILE / 4; ++k4) {
+        for (int k4 = 0; k4 < 16; ++k4) {
           const float4 kk = skv[k4];
-          const float ks[4] = {kk.x, kk.y, kk.z, kk.w};
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int k = 4 * k4 + e;
-            const float x = INT8 ? (float)(int)acc[k] : __uint_as_float(acc[k]);
-            sc[k] = x * (cq * ks[e]);
+          float f0, f1, f2, f3;
+          if (INT8) {
+            f0 = (float)(int)acc[4 * k4 + 0]; f1 = (float)(int)acc[4 * k4 + 1];
+            f2 = (float)(int)acc[4 * k4 + 2]; f3 = (float)(int)acc[4 * k4 + 3];
+          } else {
+            f0 = __uint_as_float(acc[4 * k4 + 0]); f1 = __uint_as_float(acc[4 * k4 + 1]);
+            f2 = __uint_as_float(acc[4 * k4 + 2]); f3 = __uint_as_float(acc[4 * k4 + 3]);
           }
+          u[2 * k4 + 0] = __fmul2_rn(make_float2(f0, f1), make_float2(kk.x, kk.y));
+          u[2 * k4 + 1] = __fmul2_rn(make_float2(f2, f3), make_float2(kk.z, kk.w));
         }
         // Tile-uniform mask: the diagonal tile when causal, the ragged last tile otherwise.
         if (CAUSAL) {
           if (j == q_tile) {
+            const int lim = row - 64 * half;                // local column k is masked when k > lim
 #pragma unroll
-            for (int k = 0; k < TILE; ++k) if (k > row) sc[k] = -INFINITY;
+            for (int i = 0; i < 32; ++i) {
+              if (2 * i > lim) u[i].x = -INFINITY;
+              if (2 * i + 1 > lim) u[i].y = -INFINITY;
+            }
           }
         } else {
           if ((long long)(j + 1) * TILE > a.N) {
-            const int live = (int)(a.N - (long long)j * TILE);
+            const int live = (int)(a.N - (long long)j * TILE) - 64 * half;   // local k >= live is masked
 #pragma unroll
-            for (int k = 0; k < TILE; ++k) if (k >= live) sc[k] = -INFINITY;
+            for (int i = 0; i < 32; ++i) {
+              if (2 * i >= live) u[i].x = -INFINITY;
+              if (2 * i + 1 >= live) u[i].y = -INFINITY;
+            }
           }
         }
-        float mx = sc[0];
+        float mx0 = u[0].x, mx1 = u[0].y, mx2 = u[1].x, mx3 = u[1].y;
 #pragma unroll
-        for (int k = 1; k < TILE; ++k) mx = fmaxf(mx, sc[k]);
-        const float m_new = fmaxf(m, mx);
+        for (int i = 2; i < 32; i += 4) {
+          mx0 = max3(mx0, u[i].x, u[i].y);
+          mx1 = max3(mx1, u[i + 1].x, u[i + 1].y);
+          if (i + 2 < 32) {
+            mx2 = max3(mx2, u[i + 2].x, u[i + 2].y);
+            mx3 = max3(mx3, u[i + 3].x, u[i + 3].y);
+          }
+        }
+        const float mloc = fmaxf(max3(mx0, mx1, mx2), mx3);
+        // exchange with the thread that owns the other 64 columns of this row
+        float* xrow = xch + (j & 1) * 256;
+        xrow[half * 128 + row] = mloc;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xbar);
+        ok = mbar_wait(xbar, (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (!ok) break;
+        const float m_new = max3(m, mloc, xrow[(half ^ 1) * 128 + row]);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = ex2(m - m_use);
+        const float alpha = ex2(cq * (m - m_use));
 
         if (j > 0) {
           ok = mbar_wait(bar(BAR_PV), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
@@ -376,37 +433,47 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (!ok) break;
           tc_fence_after();
           if (__any_sync(0xffffffffu, m_new > m)) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint32_t o[32];
-              tmem_ld32(t_lane + TMEM_O + 32 * i, o);
+            const float2 al2 = make_float2(alpha, alpha);
+            // 8 columns at a time: the 64 scores of this tile stay live in registers meanwhile
+#pragma unroll 1
+            for (int i = 0; i < 8; ++i) {
+              uint32_t o[8];
+              tmem_ld8(t_o + 8 * i, o);
               tmem_ld_wait();
 #pragma unroll
-              for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-              tmem_st32(t_lane + TMEM_O + 32 * i, o);
+              for (int e = 0; e < 8; e += 2) {
+                const float2 r = __fmul2_rn(make_float2(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), al2);
+                o[e] = __float_as_uint(r.x); o[e + 1] = __float_as_uint(r.y);
+              }
+              tmem_st8(t_o + 8 * i, o);
             }
             tmem_st_wait();
           }
         }
         m = m_new;
 
-        float psum = 0.f;
+        const float nm = -(cq * m_use);
+        const float2 nm2 = make_float2(nm, nm);
+        float2 ps0 = make_float2(0.f, 0.f), ps1 = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int cc = 0; cc < 8; ++cc) {                    // 16 keys = one 16-byte chunk of the P row
+        for (int cc = 0; cc < 4; ++cc) {                    // 16 keys = one 16-byte chunk of the P row
           uint32_t w[4];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
             const float4 vv = svv[4 * cc + g];
-            const float p0 = ex2(sc[16 * cc + 4 * g + 0] - m_use);
-            const float p1 = ex2(sc[16 * cc + 4 * g + 1] - m_use);
-            const float p2 = ex2(sc[16 * cc + 4 * g + 2] - m_use);
-            const float p3 = ex2(sc[16 * cc + 4 * g + 3] - m_use);
-            psum += (p0 + p1) + (p2 + p3);
-            w[g] = e4m3x4(p0 * vv.x, p1 * vv.y, p2 * vv.z, p3 * vv.w);
+            const float2 t0 = __ffma2_rn(u[8 * cc + 2 * g + 0], cq2, nm2);
+            const float2 t1 = __ffma2_rn(u[8 * cc + 2 * g + 1], cq2, nm2);
+            const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
+            const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
+            ps0 = __fadd2_rn(ps0, p01);
+            ps1 = __fadd2_rn(ps1, p23);
+            const float2 f01 = __fmul2_rn(p01, make_float2(vv.x, vv.y));
+            const float2 f23 = __fmul2_rn(p23, make_float2(vv.z, vv.w));
+            w[g] = e4m3x2(f01.x, f01.y) | (e4m3x2(f23.x, f23.y) << 16);
           }
-          *reinterpret_cast<uint4*>(p_row + ((cc ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          *reinterpret_cast<uint4*>(p_row + (((4 * half + cc) ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
         }
-        l = l * alpha + psum;
+        l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
@@ -419,15 +486,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
+        // total row sum = the two halves' sums (both were scaled with the same running max)
+        float* xrow = xch + (n_tiles & 1) * 256;
+        xrow[half * 128 + row] = l;
+        __syncwarp();
+        if (lane == 0) mbar_arrive(xbar);
+        ok = mbar_wait(xbar, (uint32_t)n_tiles & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        ok = __all_sync(0xffffffffu, ok);
+        if (ok) l += xrow[(half ^ 1) * 128 + row];
+      }
+      if (ok) {
         tc_fence_after();
         const float S = __ldg(a.s_fold + bh);
         const float inv = (l > 0.f) ? __fdiv_rn(S, __fmul_rn(l, F8_MAX)) : 0.f;
         const long long b = bh / a.H, h = bh - b * a.H;
-        OutT* orow = reinterpret_cast<OutT*>(a.out) + b * a.o_sb + h * a.o_sh + q_row * a.o_sr;
+        OutT* orow = reinterpret_cast<OutT*>(a.out) + b * a.o_sb + h * a.o_sh + q_row * a.o_sr + 64 * half;
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
+        for (int i = 0; i < 2; ++i) {
           uint32_t o[32];
-          tmem_ld32(t_lane + TMEM_O + 32 * i, o);
+          tmem_ld32(t_o + 32 * i, o);
           tmem_ld_wait();
           if (q_row < a.N) {
 #pragma unroll
