@@ -38,9 +38,9 @@ constexpr uint32_t OFF_Q = 0;
 constexpr uint32_t OFF_K = OFF_Q + TILE_BYTES;      // 2 stages
 constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;  // 2 stages
 constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;
-constexpr uint32_t OFF_SK = OFF_P + TILE_BYTES;     // 2 stages of K scales
-constexpr uint32_t OFF_SV = OFF_SK + 2 * VEC_BYTES; // 2 stages of staged V factors
-constexpr uint32_t OFF_XCH = OFF_SV + 2 * VEC_BYTES;// [parity][half][row] floats exchanged by a row's two threads
+constexpr uint32_t OFF_SK = OFF_P + TILE_BYTES;     // 4-slot ring of K scales (arrive with the K tile)
+constexpr uint32_t OFF_SV = OFF_SK + 4 * VEC_BYTES; // 4-slot ring of staged V factors (same barrier)
+constexpr uint32_t OFF_XCH = OFF_SV + 4 * VEC_BYTES;// [parity][half][row] floats exchanged by a row's two threads
 constexpr uint32_t OFF_BAR = OFF_XCH + 4 * VEC_BYTES;
 constexpr uint32_t OFF_MISC = OFF_BAR + 192;
 constexpr uint32_t SMEM_USED = OFF_MISC + 64;
@@ -100,8 +100,32 @@ __device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volat
 }
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t* cta_abort,
                                           int32_t* status, int code) {
-  if (mbar_try_wait(bar, parity)) return true;
+  // first attempt may suspend the thread in hardware for up to the hinted time (no issue slots)
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity), "r"(20000u) : "memory");
+  if (__builtin_expect(ok != 0u, 1)) return true;
   return mbar_wait_slow(bar, parity, cta_abort, status, code);
+}
+// Arrive from lane 0 only, without a branch.
+__device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, int lane) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.eq.s32 p, %1, 0;\n\t"
+      "@p mbarrier.arrive.shared::cta.b64 _, [%0];\n\t}"
+      ::"r"(bar), "r"(lane) : "memory");
+}
+// Four floats -> four e4m3 bytes in memory order (a lowest), round to nearest even, saturating.
+__device__ __forceinline__ uint32_t e4m3x4_pack(float a, float b, float c, float d) {
+  uint32_t w;
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
+      "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
+      "mov.b32 %0, {lo, hi};\n\t}"
+      : "=r"(w) : "f"(a), "f"(b), "f"(c), "f"(d));
+  return w;
 }
 
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar,
@@ -181,6 +205,37 @@ __device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// Shared-memory accesses through 32-bit shared-window addresses (half the registers of a pointer).
+#ifndef SAGE_SCALE_LD
+#define SAGE_SCALE_LD 128
+#endif
+__device__ __forceinline__ float4 lds128(uint32_t addr) {
+  float4 v;
+#if SAGE_SCALE_LD == 128
+  asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
+#elif SAGE_SCALE_LD == 64
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
+  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+8];" : "=f"(v.z), "=f"(v.w) : "r"(addr));
+#else
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v.x) : "r"(addr));
+  asm volatile("ld.shared.f32 %0, [%1+4];" : "=f"(v.y) : "r"(addr));
+  asm volatile("ld.shared.f32 %0, [%1+8];" : "=f"(v.z) : "r"(addr));
+  asm volatile("ld.shared.f32 %0, [%1+12];" : "=f"(v.w) : "r"(addr));
+#endif
+  return v;
+}
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ float lds32(uint32_t addr) {
+  float v;
+  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
+  return v;
+}
+__device__ __forceinline__ void sts32(uint32_t addr, float v) {
+  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -227,7 +282,10 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 // The kernel.  grid (ceil(N/128), B*H), block 320, two CTAs per SM.
 // ------------------------------------------------------------------------------------------------
 template <bool INT8, bool CAUSAL, typename OutT>
-__global__ void __launch_bounds__(ATT_THREADS, 2)
+#ifndef SAGE_ATT_MINBLOCKS
+#define SAGE_ATT_MINBLOCKS 2
+#endif
+__global__ void __launch_bounds__(ATT_THREADS, SAGE_ATT_MINBLOCKS)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
   extern __shared__ uint8_t smem_raw[];
@@ -284,13 +342,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           const int s = j & 1;
           const uint32_t par = ((uint32_t)(j >> 1) & 1u) ^ 1u;
           if (!mbar_wait(bar(BAR_KE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
-          mbar_expect_tx(bar(BAR_KF + s), TILE_BYTES);
+          // The tile's scale rows ride on the K barrier into a 4-slot ring: slot j&3 is rewritten
+          // only after QK(j+2) has completed, which needs every softmax warp to be past tile j.
+          mbar_expect_tx(bar(BAR_KF + s), TILE_BYTES + 2 * VEC_BYTES);
           tma_load_3d(base + OFF_K + s * TILE_BYTES, &tm_k, bar(BAR_KF + s), 0, j * TILE, bh);
+          bulk_load(base + OFF_SK + (j & 3) * VEC_BYTES, sk_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
+          bulk_load(base + OFF_SV + (j & 3) * VEC_BYTES, sv_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
           if (!mbar_wait(bar(BAR_VE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
-          mbar_expect_tx(bar(BAR_VF + s), TILE_BYTES + 2 * VEC_BYTES);
+          mbar_expect_tx(bar(BAR_VF + s), TILE_BYTES);
           tma_load_3d(base + OFF_V + s * TILE_BYTES, &tm_v, bar(BAR_VF + s), j * TILE, 0, bh);
-          bulk_load(base + OFF_SK + s * VEC_BYTES, sk_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_VF + s));
-          bulk_load(base + OFF_SV + s * VEC_BYTES, sv_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_VF + s));
         }
       }
     } else if (warp == 1) {
@@ -342,15 +402,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float2 cq2 = make_float2(cq, cq);
       float m = -INFINITY, l = 0.f;
       bool ok = true;
-      uint8_t* p_row = gbase + OFF_P + row * 128;
-      const int swz = row & 7;
-      float* xch = reinterpret_cast<float*>(gbase + OFF_XCH);      // [parity][half][row]
+      // the four 16-byte chunks of this thread's half of the P row, in the 128-byte swizzle
+      const uint32_t p_row = base + OFF_P + row * 128;
+      const uint32_t swz = (uint32_t)(row & 7) << 4;
+      const uint32_t p_c0 = p_row + ((64u * half + 0u) ^ swz), p_c1 = p_row + ((64u * half + 16u) ^ swz);
+      const uint32_t p_c2 = p_row + ((64u * half + 32u) ^ swz), p_c3 = p_row + ((64u * half + 48u) ^ swz);
+      const uint32_t x_mine = base + OFF_XCH + 4u * (half * 128 + row);          // [parity][half][row]
+      const uint32_t x_other = base + OFF_XCH + 4u * ((half ^ 1) * 128 + row);
+      const uint32_t sk_half = base + OFF_SK + 256u * half;
       const uint32_t xbar = bar(BAR_X + quarter);
 
       for (int j = 0; j < n_tiles; ++j) {
-        const int s = j & 1;
-        ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(j >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
-        if (ok) ok = mbar_wait(bar(BAR_SF), (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        // S(j) complete implies the K stage, and with it this tile's scale rows, has landed
+        ok = mbar_wait(bar(BAR_SF), (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -360,19 +424,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_SFREE));
+        mbar_arrive_lane0(bar(BAR_SFREE), lane);
         if (a.dbg != nullptr && j == a.dbg_tile) {
           uint32_t* d = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + row) * TILE + 64 * half;
 #pragma unroll
           for (int k = 0; k < 64; ++k) d[k] = acc[k];
         }
 
-        const float4* skv = reinterpret_cast<const float4*>(gbase + OFF_SK + s * VEC_BYTES) + 16 * half;
-        const float4* svv = reinterpret_cast<const float4*>(gbase + OFF_SV + s * VEC_BYTES) + 16 * half;
+        const uint32_t skv = sk_half + (uint32_t)(j & 3) * VEC_BYTES;     // this tile's 64 K scales
+        const uint32_t svv = skv + (OFF_SV - OFF_SK);                      // and its 64 staged V factors
         float2 u[32];                                       // u[i] = scores of keys 2i, 2i+1 (times sk)
 #pragma unroll
         for (int k4 = 0; k4 < 16; ++k4) {
-          const float4 kk = skv[k4];
+          const float4 kk = lds128(skv + 16 * k4);
           float f0, f1, f2, f3;
           if (INT8) {
             f0 = (float)(int)acc[4 * k4 + 0]; f1 = (float)(int)acc[4 * k4 + 1];
@@ -416,14 +480,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         const float mloc = fmaxf(max3(mx0, mx1, mx2), mx3);
         // exchange with the thread that owns the other 64 columns of this row
-        float* xrow = xch + (j & 1) * 256;
-        xrow[half * 128 + row] = mloc;
+        sts32(x_mine + (uint32_t)(j & 1) * 1024u, mloc);
         __syncwarp();
-        if (lane == 0) mbar_arrive(xbar);
+        mbar_arrive_lane0(xbar, lane);
         ok = mbar_wait(xbar, (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-        const float m_new = max3(m, mloc, xrow[(half ^ 1) * 128 + row]);
+        const float m_new = max3(m, mloc, lds32(x_other + (uint32_t)(j & 1) * 1024u));
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
         const float alpha = ex2(cq * (m - m_use));
 
@@ -460,7 +523,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           uint32_t w[4];
 #pragma unroll
           for (int g = 0; g < 4; ++g) {
-            const float4 vv = svv[4 * cc + g];
+            const float4 vv = lds128(svv + 16 * (4 * cc + g));
             const float2 t0 = __ffma2_rn(u[8 * cc + 2 * g + 0], cq2, nm2);
             const float2 t1 = __ffma2_rn(u[8 * cc + 2 * g + 1], cq2, nm2);
             const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
@@ -469,15 +532,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ps1 = __fadd2_rn(ps1, p23);
             const float2 f01 = __fmul2_rn(p01, make_float2(vv.x, vv.y));
             const float2 f23 = __fmul2_rn(p23, make_float2(vv.z, vv.w));
-            w[g] = e4m3x2(f01.x, f01.y) | (e4m3x2(f23.x, f23.y) << 16);
+            w[g] = e4m3x4_pack(f01.x, f01.y, f23.x, f23.y);
           }
-          *reinterpret_cast<uint4*>(p_row + (((4 * half + cc) ^ swz) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+          sts128(cc == 0 ? p_c0 : cc == 1 ? p_c1 : cc == 2 ? p_c2 : p_c3, w[0], w[1], w[2], w[3]);
         }
         l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_PF));
+        mbar_arrive_lane0(bar(BAR_PF), lane);
       }
 
       // ------------------------------- epilogue -----------------------------------
@@ -487,13 +550,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (ok) {
         // total row sum = the two halves' sums (both were scaled with the same running max)
-        float* xrow = xch + (n_tiles & 1) * 256;
-        xrow[half * 128 + row] = l;
+        sts32(x_mine + (uint32_t)(n_tiles & 1) * 1024u, l);
         __syncwarp();
-        if (lane == 0) mbar_arrive(xbar);
+        mbar_arrive_lane0(xbar, lane);
         ok = mbar_wait(xbar, (uint32_t)n_tiles & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
-        if (ok) l += xrow[(half ^ 1) * 128 + row];
+        if (ok) l += lds32(x_other + (uint32_t)(n_tiles & 1) * 1024u);
       }
       if (ok) {
         tc_fence_after();
