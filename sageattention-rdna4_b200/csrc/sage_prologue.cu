@@ -74,9 +74,19 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
 }
 
 // ------------------------------------------------------------------------------------------------
-// Kernel 2: quantise one 128-token tile of Q, K and V.  grid (N_pad/128, B*H), block 256.
+// Kernel 2: quantise one 128-token tile of ONE of Q, K, V.  grid (N_pad/128, B*H, 3), block 256,
+// four CTAs per SM.  blockIdx.z selects the tensor, so CTAs in different phases (load, convert,
+// store) share an SM and keep the memory system busy.
 // Thread (c = tid & 15, r0 = tid >> 4) owns columns 8c..8c+7 of rows r0, r0+16, ..., r0+112, so a
 // half-warp reads one 256-byte row with 16-byte loads and the row absmax is four shuffles.
+//
+// Division.  K and V are divided by their scale with an IEEE-correct quotient obtained as
+//   rc = rn(1/s) (correctly rounded);  q0 = rn(x*rc);  r = x - q0*s (one fma, exact);  q = fma(r, rc, q0)
+// which equals rn(x/s) whenever rc is the correctly rounded reciprocal and nothing over/underflows
+// (Markstein's theorem; |x/s| <= 448 and 1e-12 <= s here).  Three operations per element instead
+// of a full division routine; checked against true division on 8e7 random samples on the host.
+// Rounding to int8 uses the add-magic-constant trick (1.5*2^23): the addition rounds to nearest
+// even, the low byte of the sum is the two's-complement code; |x/s| <= 127 needs no clamp.
 // ------------------------------------------------------------------------------------------------
 struct QuantArgs {
   const void *q, *k, *v;
@@ -107,8 +117,21 @@ __device__ __forceinline__ void load_rows(const T* base, long long sr, long long
   }
 }
 
+// rn(x / s) given rc = rn(1/s)
+__device__ __forceinline__ float div_by_scale(float x, float s, float rc) {
+  const float q0 = __fmul_rn(x, rc);
+  const float r = -__fmaf_rn(q0, s, -x);      // x - q0*s, written so that a zero keeps x's sign
+  return __fmaf_rn(r, rc, q0);
+}
+// round-half-even of |y| < 2^22 to an int8 code, four per word (a in the low byte)
+__device__ __forceinline__ uint32_t i8x4_magic(float a, float b, float c, float d) {
+  const uint32_t ua = __float_as_uint(__fadd_rn(a, 12582912.0f)), ub = __float_as_uint(__fadd_rn(b, 12582912.0f));
+  const uint32_t uc = __float_as_uint(__fadd_rn(c, 12582912.0f)), ud = __float_as_uint(__fadd_rn(d, 12582912.0f));
+  return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
+}
+
 template <typename T, bool INT8>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(256, 4)
 quant_qkv_kernel(const QuantArgs a) {
   __shared__ __align__(16) uint32_t vt[TILE * 32];   // e4m3 V tile, [token][32 words], XOR-swizzled
   __shared__ float s_wmax[8];
@@ -116,14 +139,16 @@ quant_qkv_kernel(const QuantArgs a) {
   constexpr float QMAX = INT8 ? I8_MAX : F8_MAX;
 
   const int tid = threadIdx.x, c = tid & 15, r0 = tid >> 4, lane = tid & 31, warp = tid >> 5;
-  const int bh = blockIdx.y;
+  const int bh = gridDim.y - 1 - blockIdx.y;         // last heads first: their K is still in L2 after the mean pass
+  const int which = blockIdx.z;                      // 0 Q, 1 K, 2 V
   const long long b = bh / a.H, h = bh - b * a.H;
   const long long n_base = (long long)blockIdx.x * TILE;
   const long long N = a.N, N_pad = a.N_pad;
   uint4 raw[8];
 
-  // ---------------------------------- Q ----------------------------------
-  {
+  if (which == 0) {
+    // ---------------------------------- Q ----------------------------------
+    if (n_base >= N) return;
     const T* qb = reinterpret_cast<const T*>(a.q) + b * a.q_sb + h * a.q_sh + 8 * c;
     load_rows<T>(qb, a.q_sr, n_base, r0, N, raw);
 #pragma unroll
@@ -141,8 +166,8 @@ quant_qkv_kernel(const QuantArgs a) {
       for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(x[e], qinv);
       uint2 w;
       if (INT8) {
-        w.x = i8x4(y[0], y[1], y[2], y[3]);
-        w.y = i8x4(y[4], y[5], y[6], y[7]);
+        w.x = i8x4_magic(y[0], y[1], y[2], y[3]);
+        w.y = i8x4_magic(y[4], y[5], y[6], y[7]);
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) y[e] = fminf(fmaxf(y[e], -F8_MAX), F8_MAX);
@@ -154,10 +179,11 @@ quant_qkv_kernel(const QuantArgs a) {
         if (c == 0) a.sq[(size_t)bh * N + n] = __fdiv_rn(amax, QMAX);
       }
     }
+    return;
   }
 
-  // ---------------------------------- K ----------------------------------
-  {
+  if (which == 1) {
+    // ---------------------------------- K ----------------------------------
     const T* kb = reinterpret_cast<const T*>(a.k) + b * a.k_sb + h * a.k_sh + 8 * c;
     load_rows<T>(kb, a.k_sr, n_base, r0, N, raw);
     float mu[8];
@@ -177,13 +203,14 @@ quant_qkv_kernel(const QuantArgs a) {
       }
       amax = half_warp_max(amax);
       const float sk = fmaxf(__fdiv_rn(amax, QMAX), SCALE_FLOOR);
+      const float rc = __frcp_rn(sk);
       float y[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = __fdiv_rn(x[e], sk);
+      for (int e = 0; e < 8; ++e) y[e] = div_by_scale(x[e], sk, rc);
       uint2 w;
       if (INT8) {
-        w.x = i8x4(y[0], y[1], y[2], y[3]);
-        w.y = i8x4(y[4], y[5], y[6], y[7]);
+        w.x = i8x4_magic(y[0], y[1], y[2], y[3]);
+        w.y = i8x4_magic(y[4], y[5], y[6], y[7]);
       } else {
 #pragma unroll
         for (int e = 0; e < 8; ++e) y[e] = fminf(y[e], F8_MAX);
@@ -193,6 +220,7 @@ quant_qkv_kernel(const QuantArgs a) {
       *reinterpret_cast<uint2*>(a.k8 + ((size_t)bh * N_pad + n) * HD + 8 * c) = w;
       if (c == 0) a.sk[(size_t)bh * N_pad + n] = live ? sk : 1.0f;
     }
+    return;
   }
 
   // ---------------------------------- V ----------------------------------
@@ -212,9 +240,10 @@ quant_qkv_kernel(const QuantArgs a) {
       for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(x[e]));
       amax = half_warp_max(amax);
       const float sv = fmaxf(__fdiv_rn(amax, F8_MAX), SCALE_FLOOR);
+      const float rc = __frcp_rn(sv);
       float y[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = fminf(__fdiv_rn(x[e], sv), F8_MAX);
+      for (int e = 0; e < 8; ++e) y[e] = fminf(div_by_scale(x[e], sv, rc), F8_MAX);
       uint2 w;
       w.x = e4m3x4(y[0], y[1], y[2], y[3]);
       w.y = e4m3x4(y[4], y[5], y[6], y[7]);
@@ -314,7 +343,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   a.k_sb = p.k_strides[0]; a.k_sh = p.k_strides[1]; a.k_sr = p.k_strides[2];
   a.v_sb = p.v_strides[0]; a.v_sh = p.v_strides[1]; a.v_sr = p.v_strides[2];
   a.sub_mean = p.smooth_k ? 1 : 0;
-  dim3 grid((unsigned)(p.N_pad / TILE), (unsigned)bh);
+  dim3 grid((unsigned)(p.N_pad / TILE), (unsigned)bh, 3);
   if (p.qk_mode == 0) quant_qkv_kernel<T, true><<<grid, 256, 0, st>>>(a);
   else quant_qkv_kernel<T, false><<<grid, 256, 0, st>>>(a);
   return cudaGetLastError();

@@ -165,7 +165,7 @@ def test_video_length_properties():
     assert R.cosine(out, o128) >= COS_SAME and R.rel_l1(out, o128) <= L1_SAME
     assert R.cosine(out, o64) >= COS_REF and R.rel_l1(out, o64) <= L1_REF
     assert (out[:, 1].float() - o128[:, 1].float()).abs().max().item() < 0.05
-    assert out[:, 1].float().max().item() <= 0.7505          # never above the constant
+    assert out[:, 1].float().max().item() <= 0.75 * 1.0625    # e4m3 rounding of P can add at most one half-ulp (2^-4)
     rows = torch.tensor([0, 1, 127, 128, 5000, 23760, 47519], device="cuda")
     s = torch.matmul(q[0, 0, rows].float(), k[0, 0].float().t()) * 128 ** -0.5
     s = s.masked_fill(torch.arange(n, device="cuda")[None, :] > rows[:, None], float("-inf"))

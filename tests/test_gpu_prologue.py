@@ -48,6 +48,8 @@ def test_edge_lengths(n, dtype, smooth):
 
 def test_fp16_with_e4m3_codes():
     q, k, v = R.make_inputs(1, 2, 200, seed=8, k_bias_std=0.5)
+    k[0, 1, 8, ::5] = -0.0
+    q[0, 0, 3, ::2] = -0.0
     ref = R.prologue(q, k, v, smooth_k=True, int8=False, pad_multiple=128)
     pq = be.quant_qkv(q.cuda(), k.cuda(), v.cuda(), smooth_k=True, int8=False)
     _check_against(pq, ref, 200, True)
@@ -59,6 +61,9 @@ def test_outliers_zero_rows_and_large_v():
     k[0, 2, 5] = 0
     q[0, 3, 9] = 0
     v[0, 0, 400] = 0
+    v[0, 2, 7, ::3] = -0.0         # signed zeros must keep their sign bit in the e4m3 codes
+    k[0, 1, 8, ::5] = -0.0
+    q[0, 0, 3, ::2] = -0.0
     ref = R.prologue(q, k, v, pad_multiple=128)
     pq = be.quant_qkv(q.cuda(), k.cuda(), v.cuda())
     _check_against(pq, ref, 500, True)
