@@ -256,7 +256,7 @@ def main() -> int:
     pro_ms, att_ms = [], []
     for i in range(args.warmup + args.steps):
         ev[0].record(stream)
-        pq = be.quant_qkv(q, k, v)
+        pq = be.quant_qkv(q, k, v, reuse=pq)
         ev[1].record(stream)
         be.attn_launch(pq, o2, causal, D ** -0.5, status=st)
         ev[2].record(stream)

@@ -133,11 +133,12 @@ def _require_cuda(*ts):
 
 
 def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool = True,
-              int8: Optional[bool] = None) -> Dict[str, torch.Tensor]:
+              int8: Optional[bool] = None, reuse: Optional[dict] = None) -> Dict[str, torch.Tensor]:
     """Run the prologue on logical (B,H,N,D) views and return every tensor it writes:
     q8 (BH,N,D), sq (BH,N), k8 (BH,N_pad,D), sk (BH,N_pad), v8t (BH,D,N_pad), sv, svp (BH,N_pad),
     S (BH,), mean (BH,D) or None.  `int8=None` follows the reference's default: int8 codes for
-    fp16 inputs, e4m3 for bf16.  Code tensors are torch.int8 or torch.float8_e4m3fn."""
+    fp16 inputs, e4m3 for bf16.  Code tensors are torch.int8 or torch.float8_e4m3fn.  `reuse` is a
+    previous result for the same shapes whose buffers are written again instead of allocating."""
     _require_cuda(q, k, v)
     lib = _native.load()
     b, h, n, d = q.shape
@@ -147,22 +148,27 @@ def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool 
     code_dt = torch.int8 if int8 else torch.float8_e4m3fn
     u8 = dict(dtype=torch.uint8, device=dev)
     f32 = dict(dtype=torch.float32, device=dev)
-    out = dict(
-        q8=torch.empty((bh, n, d), **u8), sq=torch.empty((bh, n), **f32),
-        k8=torch.empty((bh, n_pad, d), **u8), sk=torch.empty((bh, n_pad), **f32),
-        v8t=torch.empty((bh, d, n_pad), **u8), sv=torch.empty((bh, n_pad), **f32),
-        svp=torch.empty((bh, n_pad), **f32), S=torch.empty((bh,), **f32),
-        mean=torch.empty((bh, d), **f32) if smooth_k else None)
-    ctrl = torch.empty((lib.sage_prologue_ctrl_bytes(b, h, n),), **u8)
+    if reuse is not None and (reuse["B"], reuse["H"], reuse["n"], reuse["int8"]) == (b, h, n, bool(int8)) \
+            and (reuse["mean"] is not None) == bool(smooth_k):
+        out = dict(reuse)
+        for key in ("q8", "k8", "v8t"):
+            out[key] = out[key].view(torch.uint8)
+    else:
+        out = dict(
+            q8=torch.empty((bh, n, d), **u8), sq=torch.empty((bh, n), **f32),
+            k8=torch.empty((bh, n_pad, d), **u8), sk=torch.empty((bh, n_pad), **f32),
+            v8t=torch.empty((bh, d, n_pad), **u8), sv=torch.empty((bh, n_pad), **f32),
+            svp=torch.empty((bh, n_pad), **f32), S=torch.empty((bh,), **f32),
+            mean=torch.empty((bh, d), **f32) if smooth_k else None,
+            ctrl=torch.empty((lib.sage_prologue_ctrl_bytes(b, h, n),), **u8))
     with torch.cuda.device(dev):
         rc = lib.sage_prologue(
             _ptr(q), _ptr(k), _ptr(v), _ptr(out["q8"]), _ptr(out["sq"]), _ptr(out["k8"]),
             _ptr(out["sk"]), _ptr(out["v8t"]), _ptr(out["sv"]), _ptr(out["svp"]), _ptr(out["S"]),
-            _ptr(out["mean"]), _ptr(ctrl), b, h, n, n_pad, _bhr(q), _bhr(k), _bhr(v),
+            _ptr(out["mean"]), _ptr(out["ctrl"]), b, h, n, n_pad, _bhr(q), _bhr(k), _bhr(v),
             _dtype_code(q.dtype), _native.SAGE_QK_INT8 if int8 else _native.SAGE_QK_E4M3,
             1 if smooth_k else 0, _stream(dev))
     _native.check(rc, "sage_prologue")
-    ctrl.record_stream(torch.cuda.current_stream(dev))
     out["q8"] = out["q8"].view(code_dt)
     out["k8"] = out["k8"].view(code_dt)
     out["v8t"] = out["v8t"].view(torch.float8_e4m3fn)
