@@ -78,6 +78,32 @@ int sage_prologue(const void* q, const void* k, const void* v,
                   const int64_t v_strides[3],
                   int dtype, int qk_mode, int smooth_k, void* stream);
 
+/* The prologue for callers that must not allocate.  It has no counterpart in the reference.
+ *
+ * Same work and same results as sage_prologue, but the `ctrl` scratch is not passed in: it is a
+ * 1 MiB array built into the library's device image (sage_prologue_static_ctrl_capacity() bytes;
+ * every GPU that loads the library holds it until the process exits).  Meant for hosts that may
+ * not call cudaMalloc where they run the prologue -- a plugin's enqueue step that only gets
+ * pre-assigned buffers, a serving process under a hard memory cap, a latency path that cannot
+ * take cudaMalloc's implicit synchronisation.  The function calls no cudaMalloc, no cudaFree and
+ * no allocating library routine; inputs and outputs are still the caller's.
+ *   - Shapes whose scratch need (sage_prologue_ctrl_bytes) exceeds the capacity are refused with
+ *     SAGE_E_UNSUPPORTED and a message; nothing is launched.
+ *   - The first call on each device looks up the array's device address (the device must be
+ *     current); make that first call before starting any stream capture.
+ *   - All calls on a device share the one array, and it keeps the previous call's contents; the
+ *     words that must start at zero are cleared on the stream at the start of each call.  Two
+ *     calls whose GPU work overlaps (different streams, no ordering between them) race on it:
+ *     order them, or give one of them its own scratch through sage_prologue. */
+size_t sage_prologue_static_ctrl_capacity(void);
+int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
+                              void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv,
+                              float* svp, float* s_fold, float* mean,
+                              int64_t B, int64_t H, int64_t N, int64_t N_pad,
+                              const int64_t q_strides[3], const int64_t k_strides[3],
+                              const int64_t v_strides[3],
+                              int dtype, int qk_mode, int smooth_k, void* stream);
+
 /* The attention kernel on quantised operands.
  *
  * Replaces Sk1Attn.launch / launch_strided (sageattention/sk1_backend/sk1_loader.py:628-688) and

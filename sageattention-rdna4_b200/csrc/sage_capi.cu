@@ -1,6 +1,8 @@
 // extern "C" boundary of libsage_b200.so (declared in include/sage_b200.h): argument checks,
 // workspace carving and the two launches.  Nothing here allocates or synchronises.
 #include <stdarg.h>
+
+#include <mutex>
 #include <stdio.h>
 #include <string.h>
 
@@ -18,6 +20,40 @@ int fail(int code, const char* fmt, ...) {
   vsnprintf(g_err, sizeof(g_err), fmt, ap);
   va_end(ap);
   return code;
+}
+
+// ---- built-in control scratch for sage_prologue_static_ctrl ------------------------------------
+// Some hosts may not call an allocator at all at the point where they run the prologue: a plugin
+// whose enqueue step is handed a fixed set of buffers, a serving process pinned under a memory
+// cap, code on a path where cudaMalloc's implicit device synchronisation is unacceptable.  For
+// them the prologue's scratch (per-head arrival counters, the running maximum of the V scale and
+// the fp64 partial sums of the mean) lives in this file-scope device array instead of in
+// caller-owned memory.  Every GPU that loads the library carries the array until the process
+// exits.  In host code the array's name is only a handle: the device address is obtained once per
+// device with cudaGetSymbolAddress and that pointer is what the kernels receive.
+constexpr size_t kStaticCtrlBytes = (size_t)1 << 20;                  // 1 MiB
+static __device__ __align__(256) unsigned char g_static_ctrl[kStaticCtrlBytes];
+
+constexpr int kMaxDevices = 64;
+std::mutex g_static_ctrl_mutex;
+void* g_static_ctrl_ptr[kMaxDevices] = {nullptr};
+
+// Device address of the built-in block on the CURRENT device (looked up on first use there).
+int static_ctrl_address(void** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return fail(SAGE_E_UNSUPPORTED, "device ordinal %d is out of range", dev);
+  std::lock_guard<std::mutex> lock(g_static_ctrl_mutex);
+  if (g_static_ctrl_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, g_static_ctrl);
+    if (e != cudaSuccess || p == nullptr)
+      return fail(SAGE_E_CUDA, "cudaGetSymbolAddress(built-in control scratch): %s", cudaGetErrorString(e));
+    g_static_ctrl_ptr[dev] = p;
+  }
+  *out = g_static_ctrl_ptr[dev];
+  return SAGE_OK;
 }
 
 inline size_t align256(size_t x) { return (x + 255) / 256 * 256; }
@@ -108,6 +144,30 @@ int sage_prologue(const void* q, const void* k, const void* v,
   cudaError_t e = sage::launch_prologue(p, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(SAGE_E_CUDA, "sage_prologue: %s", cudaGetErrorString(e));
   return SAGE_OK;
+}
+
+size_t sage_prologue_static_ctrl_capacity(void) { return kStaticCtrlBytes; }
+
+int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
+                              void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv,
+                              float* svp, float* s_fold, float* mean,
+                              int64_t B, int64_t H, int64_t N, int64_t N_pad,
+                              const int64_t q_strides[3], const int64_t k_strides[3],
+                              const int64_t v_strides[3],
+                              int dtype, int qk_mode, int smooth_k, void* stream) {
+  g_err[0] = 0;
+  int rc = check_dims(B, H, N);
+  if (rc) return rc;
+  const size_t need = sage::prologue_ctrl_bytes(B, H, N);
+  if (need > kStaticCtrlBytes)
+    return fail(SAGE_E_UNSUPPORTED,
+                "sage_prologue_static_ctrl: this shape needs %zu bytes of control scratch, the built-in block "
+                "holds %zu; use sage_prologue with caller-owned scratch", need, (size_t)kStaticCtrlBytes);
+  void* ctrl = nullptr;
+  rc = static_ctrl_address(&ctrl);
+  if (rc) return rc;
+  return sage_prologue(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, B, H, N, N_pad,
+                       q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream);
 }
 
 int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* sk,

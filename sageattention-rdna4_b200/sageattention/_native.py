@@ -31,6 +31,10 @@ SIGNATURES = {
     "sage_prologue": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                      _I64, _I64, _I64, _I64, _S3, _S3, _S3,
                                      ctypes.c_int, ctypes.c_int, ctypes.c_int, _P]),
+    "sage_prologue_static_ctrl_capacity": (ctypes.c_size_t, []),
+    "sage_prologue_static_ctrl": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                                 _I64, _I64, _I64, _I64, _S3, _S3, _S3,
+                                                 ctypes.c_int, ctypes.c_int, ctypes.c_int, _P]),
     "sage_attn_fwd": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P,
                                      _I64, _I64, _I64, _I64, _S3,
                                      ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int, _P, _P]),
