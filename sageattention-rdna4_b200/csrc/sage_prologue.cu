@@ -44,7 +44,7 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
   double acc[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.0;
-#pragma unroll 4
+#pragma unroll 8
   for (long long n = n0 + r; n < n1; n += 16) {
     const uint4 u = __ldg(reinterpret_cast<const uint4*>(base + n * sr));
     float x[8];
@@ -140,7 +140,7 @@ quant_qkv_kernel(const QuantArgs a) {
 
   const int tid = threadIdx.x, c = tid & 15, r0 = tid >> 4, lane = tid & 31, warp = tid >> 5;
   const int bh = gridDim.y - 1 - blockIdx.y;         // last heads first: their K is still in L2 after the mean pass
-  const int which = blockIdx.z;                      // 0 Q, 1 K, 2 V
+  const int which = blockIdx.z == 0 ? 1 : (blockIdx.z == 1 ? 0 : 2);   // 0 Q, 1 K, 2 V; K tiles are issued first
   const long long b = bh / a.H, h = bh - b * a.H;
   const long long n_base = (long long)blockIdx.x * TILE;
   const long long N = a.N, N_pad = a.N_pad;
