@@ -495,24 +495,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
-          if (__any_sync(0xffffffffu, m_new > m)) {
-            const float2 al2 = make_float2(alpha, alpha);
-            // 8 columns at a time: the 64 scores of this tile stay live in registers meanwhile
-#pragma unroll 1
-            for (int i = 0; i < 8; ++i) {
-              uint32_t o[8];
-              tmem_ld8(t_o + 8 * i, o);
-              tmem_ld_wait();
-#pragma unroll
-              for (int e = 0; e < 8; e += 2) {
-                const float2 r = __fmul2_rn(make_float2(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), al2);
-                o[e] = __float_as_uint(r.x); o[e + 1] = __float_as_uint(r.y);
-              }
-              tmem_st8(t_o + 8 * i, o);
-            }
-            tmem_st_wait();
-          }
         }
+        // The accumulator is rescaled after the exponentials, when the score registers are free
+        // (two TMEM round trips of 32 columns); PV(j) is not issued before this warp arrives.
+        const bool rescale = (j > 0) && __any_sync(0xffffffffu, m_new > m);
         m = m_new;
 
         const float nm = -(cq * m_use);
@@ -537,6 +523,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           sts128(cc == 0 ? p_c0 : cc == 1 ? p_c1 : cc == 2 ? p_c2 : p_c3, w[0], w[1], w[2], w[3]);
         }
         l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
+        if (rescale) {
+          const float2 al2 = make_float2(alpha, alpha);
+#pragma unroll 1
+          for (int i = 0; i < 2; ++i) {
+            uint32_t o[32];
+            tmem_ld32(t_o + 32 * i, o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; e += 2) {
+              const float2 r = __fmul2_rn(make_float2(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), al2);
+              o[e] = __float_as_uint(r.x); o[e + 1] = __float_as_uint(r.y);
+            }
+            tmem_st32(t_o + 32 * i, o);
+          }
+          tmem_st_wait();
+        }
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
