@@ -152,6 +152,49 @@ def cpu_baseline(causal: bool, rows: int = 0) -> dict:
                        "%d keys = %.2e of the call's flops, %.1f s" % (H, rows, row0, int(keys), fl / flops(causal), dt))
 
 
+def other_arms(q, k, v, dev, causal_main: bool) -> dict:
+    """Full-call numbers for the arms the headline does not cover: the other masking mode, bf16
+    inputs (e4m3 Q.K), and the short-call sweep of the configurations (fp16, H=48, non-causal,
+    N in 288..4096, every call timed alone between two synchronisations, median of 20)."""
+    import sageattention
+
+    def timed(fn, iters):
+        fn(); fn()
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(iters):
+            fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) / iters
+
+    out = {}
+    ms = timed(lambda: sageattention.sageattn(q, k, v, is_causal=not causal_main), 3)
+    out["fp16_%s" % ("causal" if not causal_main else "non_causal")] = dict(
+        ms=ms, tflops=flops(not causal_main) / (ms * 1e-3) / 1e12)
+    qb, kb, vb = q.to(torch.bfloat16), k.to(torch.bfloat16), v.to(torch.bfloat16)
+    for c in (False, True):
+        ms = timed(lambda: sageattention.sageattn(qb, kb, vb, is_causal=c), 3)
+        out["bf16_%s" % ("causal" if c else "non_causal")] = dict(ms=ms, tflops=flops(c) / (ms * 1e-3) / 1e12)
+    del qb, kb, vb
+    short = {}
+    for n in (288, 512, 1024, 4096):
+        qs, ks, vs = (t[:, :, :n].contiguous() for t in (q, k, v))
+        sageattention.sageattn(qs, ks, vs)
+        samples = []
+        for _ in range(20):
+            torch.cuda.synchronize(dev)
+            t0 = time.perf_counter()
+            sageattention.sageattn(qs, ks, vs)
+            torch.cuda.synchronize(dev)
+            samples.append((time.perf_counter() - t0) * 1e3)
+        med = statistics.median(samples)
+        short[str(n)] = dict(ms=med, tflops=4.0 * H * n * n * D / (med * 1e-3) / 1e12)
+    out["short_calls_fp16_non_causal_wall_clock"] = short
+    return out
+
+
 def run_reference(args) -> int:
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
@@ -189,6 +232,7 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the causal / bf16 / short-call arms")
     ap.add_argument("--shape", default=None, metavar="H,N",
                     help="override heads and sequence length (profiling captures on a smaller case)")
     args = ap.parse_args()
@@ -299,6 +343,11 @@ def main() -> int:
     e2e = dict(value=flops(causal, B * world) / (e2e_ms * 1e-3) / 1e12, unit="TFLOP/s", ms_per_step=e2e_ms,
                h2d_bytes_per_step=3 * nbytes, d2h_bytes_per_step=nbytes)
 
+    # ---- the other arms of the configurations (informative; N = 1 only) ----
+    others = None
+    if world == 1 and not args.no_extras and not args.shape:
+        others = other_arms(q, k, v, dev, causal)
+
     if world > 1:
         dist.barrier()
     if rank == 0:
@@ -307,6 +356,8 @@ def main() -> int:
                     dtype="int8+fp8", data="synthetic", config=workload_config(causal, world),
                     roofline=roofline, prologue=prologue, e2e=e2e, gpu_launches=3 * args.steps,
                     clocks=clk.summary(), kernel_status=status)
+        if others is not None:
+            line["other_arms"] = others
         if not args.no_cpu_baseline and world == 1:
             line["cpu_baseline"] = cpu_baseline(causal)
         print(json.dumps(line))

@@ -31,7 +31,7 @@
 
 namespace sage {
 
-constexpr int ATT_THREADS = 320;
+constexpr int ATT_THREADS = 384;                    // 3 warpgroups: {TMA, MMA, 2 idle warps}, 2 x softmax
 constexpr uint32_t TILE_BYTES = TILE * HD;          // 16 KiB: 128 rows x 128 one-byte codes
 constexpr uint32_t VEC_BYTES = TILE * 4;            // 128 floats
 constexpr uint32_t OFF_Q = 0;
@@ -81,7 +81,7 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 }
 // Bounded wait.  Returns false when it gave up (its own time limit, or a failure flagged by
 // someone else); the caller then leaves its loop.
-__device__ __noinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* cta_abort,
+__device__ __forceinline__ bool mbar_wait_slow(uint32_t bar, uint32_t parity, volatile uint32_t* cta_abort,
                                             int32_t* status, int code) {
   const long long t0 = clock64();
   uint32_t it = 0;
@@ -329,7 +329,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem = misc[0];
   const bool skip_all = misc[1] != 0u;
 
+  // Registers move from the producer/MMA warpgroup to the two softmax warpgroups:
+  // 384 x 80 at launch = 128 x 32 + 256 x 104 afterwards.
   if (!skip_all) {
+    if (warp < 4) {
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+    }
     if (warp == 0) {
       // ------------------------------- TMA producer -------------------------------
       if (lane == 0) {
@@ -388,10 +393,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-    } else {
+    } else if (warp >= 4) {
       // ------------------------------- softmax warps ------------------------------
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
       const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
-      const int half = (warp - 2) >> 2;                     // which 64 key columns of the tile
+      const int half = (warp - 4) >> 2;                     // which 64 key columns of the tile
       const int row = 32 * quarter + lane;                  // TMEM lane == query row of the tile
       const long long q_row = (long long)q_tile * TILE + row;
       const uint32_t t_s = tmem + ((uint32_t)(32 * quarter) << 16) + 64 * half;
@@ -644,8 +650,17 @@ template <bool INT8, bool CAUSAL, typename OutT>
 static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                                const AttnKArgs& ka, dim3 grid, cudaStream_t st) {
   auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT>;
-  cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+  // the opt-in to more than 48 KB of dynamic shared memory is per device and per instantiation;
+  // it is made once (short calls are dominated by host-side work)
+  static bool opted_in[64] = {false};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64 || !opted_in[dev]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64) opted_in[dev] = true;
+  }
   kern<<<grid, ATT_THREADS, SMEM_BYTES, st>>>(mq, mk, mv, ka);
   return cudaGetLastError();
 }
