@@ -1,12 +1,14 @@
 // Quantised flash attention for B200 (sm_100a): tcgen05 tensor cores, TMEM accumulators, TMA tiles.
 //
 // One CTA owns 128 queries of one (batch, head) and streams 128-key tiles; two CTAs share an SM so
-// that one CTA's softmax overlaps the other's matrix products.  Roles inside a CTA (320 threads):
-//   warp 0     TMA producer: Q tile once, then a 2-deep ring of K tiles and a 2-deep ring of
-//              V^T tiles, each V stage carrying that tile's 128 K scales and 128 staged V factors
+// that one CTA's softmax overlaps the other's matrix products.  Roles inside a CTA (384 threads):
+//   warp 0     TMA producer: Q tile once, then a 2-deep ring of K tiles (each carrying that tile's
+//              128 K scales and 128 staged V factors into a 4-slot ring) and a 2-deep ring of
+//              V^T tiles
 //   warp 1     allocates 256 TMEM columns; one thread issues every tcgen05.mma
-//   warps 2-9  softmax: two threads per query row (TMEM lane = row); warps 2-5 take key columns
-//              0..63 of the tile, warps 6-9 columns 64..127; a pair exchanges its row maximum
+//   warps 2-3  idle: they complete the first warpgroup, whose registers setmaxnreg hands over
+//   warps 4-11 softmax: two threads per query row (TMEM lane = row); warps 4-7 take key columns
+//              0..63 of the tile, warps 8-11 columns 64..127; a pair exchanges its row maximum
 //              through shared memory and a two-arrival mbarrier
 // Per key tile j:
 //   S  = Q8 . K8^T          kind::i8 (s32) or kind::f8f6f4 (f32), M=N=K=128, into TMEM cols 0..127
@@ -120,10 +122,12 @@ __device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, int lane) {
 // Four floats -> four e4m3 bytes in memory order (a lowest), round to nearest even, saturating.
 __device__ __forceinline__ uint32_t e4m3x4_pack(float a, float b, float c, float d) {
   uint32_t w;
-  asm("{\n\t.reg .b16 lo, hi;\n\t"
+  asm("{\n\t.reg .b16 lo, hi;\n\t.reg .b32 l32, h32;\n\t"
       "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
       "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
-      "mov.b32 %0, {lo, hi};\n\t}"
+      "cvt.u32.u16 l32, lo;\n\t"
+      "cvt.u32.u16 h32, hi;\n\t"
+      "prmt.b32 %0, l32, h32, 0x5410;\n\t}"
       : "=r"(w) : "f"(a), "f"(b), "f"(c), "f"(d));
   return w;
 }
@@ -279,7 +283,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 }
 
 // ------------------------------------------------------------------------------------------------
-// The kernel.  grid (ceil(N/128), B*H), block 320, two CTAs per SM.
+// The kernel.  grid (ceil(N/128), B*H), block 384, two CTAs per SM.
 // ------------------------------------------------------------------------------------------------
 template <bool INT8, bool CAUSAL, typename OutT>
 #ifndef SAGE_ATT_MINBLOCKS
