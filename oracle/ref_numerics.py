@@ -163,7 +163,7 @@ def row_score_scale(sq: torch.Tensor, sm_scale: float) -> torch.Tensor:
 def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tensor,
            v8: torch.Tensor, svp: torch.Tensor, s_fold: torch.Tensor, n: int, causal: bool,
            sm_scale: float, out_dtype: torch.dtype, tile: int = REF_BN,
-           row_chunk: int = 2048, row0: int = 0) -> torch.Tensor:
+           row_chunk: int = 2048, row0: int = 0, return_lse: bool = False):
     """The attention loop of sk1_t6i.hip:151-299 on already-quantised operands.
 
     q8 (B,H,R,D), sq (B,H,R) hold the query rows row0 .. row0+R-1 (all N rows by default); k8, v8
@@ -173,19 +173,31 @@ def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tenso
     mask, one running-max update per tile, p = exp2(s - m), l = l*alpha + sum(p) taken BEFORE
     the fold, p8 = e4m3(p * f32(svp*448)), acc = acc*alpha + p8 @ v8 in fp32; epilogue
     acc * (S / (l*448)).  `exp2` here is torch's, the kernels use hardware approximations: the
-    output is a tolerance target, not a bit target."""
+    output is a tolerance target, not a bit target.
+
+    Beyond the reference's hand-written path (which refuses these shapes): k8/v8 may have fewer
+    heads than q8 (grouped-query attention; every group of Hq/Hkv query heads shares a K/V head),
+    the number of keys may differ from the number of queries when not causal, and with
+    `return_lse` the function also returns ln2 * (m + log2 l), the log-sum-exp of the
+    mean-subtracted logits (callers add sm_scale * q.mean(K) for the caller's K)."""
     prev_tf32 = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
         b, h, nq, d = q8.shape
         n_pad = k8.shape[2]
-        assert n_pad % tile == 0 and row0 + nq <= n
+        assert n_pad % tile == 0 and (not causal or row0 + nq <= n)
+        if k8.shape[1] != h:                                  # grouped-query attention
+            g = h // k8.shape[1]
+            k8, v8 = k8.repeat_interleave(g, dim=1), v8.repeat_interleave(g, dim=1)
+            sk, svp = sk.repeat_interleave(g, dim=1), svp.repeat_interleave(g, dim=1)
+            s_fold = s_fold.repeat_interleave(g, dim=1)
         dev = q8.device
         kf = k8.float()
         vf = v8.float()
         stage = stage_sv(svp)
         cq_all = row_score_scale(sq, sm_scale)
         out = torch.empty(b, h, nq, d, dtype=out_dtype, device=dev)
+        lse = torch.empty(b, h, nq, dtype=torch.float32, device=dev)
         neg_inf = _f32(float("-inf"), dev)
         for r0 in range(0, nq, row_chunk):
             r1 = min(nq, r0 + row_chunk)
@@ -217,7 +229,8 @@ def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tenso
                 acc = acc * alpha[..., None] + torch.matmul(p8, vf[:, :, c0:c1])
             inv = torch.where(l > 0, s_fold[..., None] / (l * _f32(F8_MAX, dev)), torch.zeros_like(l))
             out[:, :, r0:r1] = (acc * inv[..., None]).to(out_dtype)
-        return out
+            lse[:, :, r0:r1] = math.log(2.0) * (m + torch.log2(l))
+        return (out, lse) if return_lse else out
     finally:
         torch.backends.cuda.matmul.allow_tf32 = prev_tf32
 
@@ -243,7 +256,7 @@ def prologue(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool =
 def sageattn_oracle(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                     is_causal: bool = False, sm_scale: Optional[float] = None,
                     smooth_k: bool = True, int8: Optional[bool] = None,
-                    tile: int = REF_BN) -> torch.Tensor:
+                    tile: int = REF_BN, return_lse: bool = False):
     """The reference call end to end (sageattention/sk1_backend/__init__.py:982-1284): output has
     q's shape, dtype and layout; sm_scale defaults to D**-0.5 (:1165)."""
     if tensor_layout == "NHD":
@@ -254,22 +267,33 @@ def sageattn_oracle(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_la
     if sm_scale is None:
         sm_scale = d ** -0.5
     pq = prologue(q, k, v, smooth_k=smooth_k, int8=int8, pad_multiple=tile)
-    out = attend(pq["q8"], pq["sq"], pq["k8"], pq["sk"], pq["v8"], pq["svp"], pq["S"], pq["n"],
-                 is_causal, float(sm_scale), q.dtype, tile=tile)
+    res = attend(pq["q8"], pq["sq"], pq["k8"], pq["sk"], pq["v8"], pq["svp"], pq["S"], pq["n"],
+                 is_causal, float(sm_scale), q.dtype, tile=tile, return_lse=return_lse)
+    out = res[0] if return_lse else res
     if tensor_layout == "NHD":
         out = out.transpose(1, 2)
-    return out
+    if not return_lse:
+        return out
+    lse = res[1]
+    if smooth_k:   # the logits of the caller's K differ from the mean-subtracted ones by q.mean per row
+        g = q.shape[1] // k.shape[1]
+        mean = pq["mean"].repeat_interleave(g, dim=1) if g > 1 else pq["mean"]
+        lse = lse + float(sm_scale) * torch.einsum("bhnd,bhd->bhn", q.float(), mean)
+    return out, lse
 
 
 def sdpa_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool = False,
-              sm_scale: Optional[float] = None, row_chunk: int = 4096) -> torch.Tensor:
+              sm_scale: Optional[float] = None, row_chunk: int = 4096, return_lse: bool = False):
     """Exact-attention comparator, the reference's own oracle (tests/test_sk1_backend.py:51-52),
     evaluated in query-row chunks so that no N x N matrix beyond `row_chunk` rows exists."""
     b, h, n, d = q.shape
     scale = d ** -0.5 if sm_scale is None else sm_scale
     qf, kf, vf = q.float(), k.float(), v.float()
+    if kf.shape[1] != h:
+        kf, vf = kf.repeat_interleave(h // kf.shape[1], dim=1), vf.repeat_interleave(h // vf.shape[1], dim=1)
     out = torch.empty(b, h, n, d, dtype=torch.float32, device=q.device)
-    keys = torch.arange(n, device=q.device)
+    lse = torch.empty(b, h, n, dtype=torch.float32, device=q.device)
+    keys = torch.arange(kf.shape[2], device=q.device)
     for r0 in range(0, n, row_chunk):
         r1 = min(n, r0 + row_chunk)
         s = torch.matmul(qf[:, :, r0:r1], kf.transpose(2, 3)) * scale
@@ -277,7 +301,8 @@ def sdpa_fp32(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causal: bool
             rows = torch.arange(r0, r1, device=q.device)
             s = s.masked_fill(keys[None, :] > rows[:, None], float("-inf"))
         out[:, :, r0:r1] = torch.matmul(torch.softmax(s, dim=-1), vf)
-    return out
+        lse[:, :, r0:r1] = torch.logsumexp(s, dim=-1)
+    return (out, lse) if return_lse else out
 
 
 # ---- error metrics used by the tests and the reports -------------------------------------------

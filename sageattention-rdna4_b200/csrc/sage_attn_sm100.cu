@@ -264,7 +264,10 @@ constexpr uint32_t IDESC_F8 = (1u << 4) | (0u << 7) | (0u << 10) | ((128u >> 3) 
 struct AttnKArgs {
   const float *sq, *sk, *svp, *s_fold;
   void* out;
-  long long N, N_pad, H;
+  long long N, N_pad, H;          // keys: length, padded length, K/V heads per batch element
+  long long Nq, Hq, group;        // queries: length, heads per batch element, Hq / H
+  float* lse;                     // optional (B*Hq, Nq)
+  const float* qm;                // optional: dot(q row, K mean), added to the LSE (times sm_scale)
   long long o_sb, o_sh, o_sr;
   float sm_scale;
   int32_t* status;
@@ -303,7 +306,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int q_tile = CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // longest first
-  const int bh = blockIdx.y;
+  const int bh = blockIdx.y;                          // (batch, query head)
+  const int bh_kv = (int)((bh / a.Hq) * a.H + (bh % a.Hq) / a.group);   // its (batch, K/V head)
   const int n_tiles = CAUSAL ? (q_tile + 1) : (int)(a.N_pad / TILE);
 
   if (tid == 0) {
@@ -345,8 +349,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         prefetch_map(&tm_q); prefetch_map(&tm_k); prefetch_map(&tm_v);
         mbar_expect_tx(bar(BAR_Q), TILE_BYTES);
         tma_load_3d(base + OFF_Q, &tm_q, bar(BAR_Q), 0, q_tile * TILE, bh);
-        const float* sk_row = a.sk + (size_t)bh * a.N_pad;
-        const float* sv_row = a.svp + (size_t)bh * a.N_pad;
+        const float* sk_row = a.sk + (size_t)bh_kv * a.N_pad;
+        const float* sv_row = a.svp + (size_t)bh_kv * a.N_pad;
         for (int j = 0; j < n_tiles; ++j) {
           const int s = j & 1;
           const uint32_t par = ((uint32_t)(j >> 1) & 1u) ^ 1u;
@@ -354,12 +358,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           // The tile's scale rows ride on the K barrier into a 4-slot ring: slot j&3 is rewritten
           // only after QK(j+2) has completed, which needs every softmax warp to be past tile j.
           mbar_expect_tx(bar(BAR_KF + s), TILE_BYTES + 2 * VEC_BYTES);
-          tma_load_3d(base + OFF_K + s * TILE_BYTES, &tm_k, bar(BAR_KF + s), 0, j * TILE, bh);
+          tma_load_3d(base + OFF_K + s * TILE_BYTES, &tm_k, bar(BAR_KF + s), 0, j * TILE, bh_kv);
           bulk_load(base + OFF_SK + (j & 3) * VEC_BYTES, sk_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
           bulk_load(base + OFF_SV + (j & 3) * VEC_BYTES, sv_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
           if (!mbar_wait(bar(BAR_VE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
           mbar_expect_tx(bar(BAR_VF + s), TILE_BYTES);
-          tma_load_3d(base + OFF_V + s * TILE_BYTES, &tm_v, bar(BAR_VF + s), j * TILE, 0, bh);
+          tma_load_3d(base + OFF_V + s * TILE_BYTES, &tm_v, bar(BAR_VF + s), j * TILE, 0, bh_kv);
         }
       }
     } else if (warp == 1) {
@@ -407,8 +411,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t t_s = tmem + ((uint32_t)(32 * quarter) << 16) + 64 * half;
       const uint32_t t_o = t_s + TMEM_O;
       // c_q = f32(f32(sm_scale * log2e) * sq); rows past N get 1 (their scores are all zero)
-      const float cq = (q_row < a.N)
-          ? __fmul_rn(__fmul_rn(a.sm_scale, LOG2E_F), __ldg(a.sq + (size_t)bh * a.N + q_row)) : 1.f;
+      const float cq = (q_row < a.Nq)
+          ? __fmul_rn(__fmul_rn(a.sm_scale, LOG2E_F), __ldg(a.sq + (size_t)bh * a.Nq + q_row)) : 1.f;
       const float2 cq2 = make_float2(cq, cq);
       float m = -INFINITY, l = 0.f;
       bool ok = true;
@@ -571,16 +575,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
       if (ok) {
         tc_fence_after();
-        const float S = __ldg(a.s_fold + bh);
+        const float S = __ldg(a.s_fold + bh_kv);
         const float inv = (l > 0.f) ? __fdiv_rn(S, __fmul_rn(l, F8_MAX)) : 0.f;
-        const long long b = bh / a.H, h = bh - b * a.H;
+        const long long b = bh / a.Hq, h = bh - b * a.Hq;
+        if (a.lse != nullptr && half == 0 && q_row < a.Nq) {
+          // ln sum_k exp(q.k*sm_scale) = ln2 * (c_q*m + log2 l) (+ q.mean*sm_scale with smooth_k)
+          float v = (l > 0.f) ? 0.6931471805599453f * (cq * m + log2f(l)) : -INFINITY;
+          if (a.qm != nullptr) v += a.sm_scale * __ldg(a.qm + (size_t)bh * a.Nq + q_row);
+          a.lse[(size_t)bh * a.Nq + q_row] = v;
+        }
         OutT* orow = reinterpret_cast<OutT*>(a.out) + b * a.o_sb + h * a.o_sh + q_row * a.o_sr + 64 * half;
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
           uint32_t o[32];
           tmem_ld32(t_o + 32 * i, o);
           tmem_ld_wait();
-          if (q_row < a.N) {
+          if (q_row < a.Nq) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
               uint4 w;
@@ -670,9 +680,10 @@ static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, con
 }
 
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why) {
-  const uint64_t bh = (uint64_t)(p.B * p.H), N = (uint64_t)p.N, N_pad = (uint64_t)p.N_pad;
+  const uint64_t bh = (uint64_t)(p.B * p.H), N_pad = (uint64_t)p.N_pad;
+  const uint64_t bhq = (uint64_t)(p.B * p.Hq), Nq = (uint64_t)p.Nq;
   CUtensorMap mq, mk, mv;
-  if (!make_map(&mq, p.q8, HD, N, bh, HD, N * HD) ||
+  if (!make_map(&mq, p.q8, HD, Nq, bhq, HD, Nq * HD) ||
       !make_map(&mk, p.k8, HD, N_pad, bh, HD, N_pad * HD) ||
       !make_map(&mv, p.v8t, N_pad, HD, bh, N_pad, N_pad * HD)) {
     if (why) *why = "cuTensorMapEncodeTiled failed (driver entry point missing or bad operand layout)";
@@ -681,10 +692,11 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   AttnKArgs ka;
   ka.sq = p.sq; ka.sk = p.sk; ka.svp = p.svp; ka.s_fold = p.s_fold; ka.out = p.out;
   ka.N = p.N; ka.N_pad = p.N_pad; ka.H = p.H;
+  ka.Nq = p.Nq; ka.Hq = p.Hq; ka.group = p.Hq / p.H; ka.lse = p.lse; ka.qm = p.qm;
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
   ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;
-  dim3 grid((unsigned)((p.N + TILE - 1) / TILE), (unsigned)bh);
+  dim3 grid((unsigned)((p.Nq + TILE - 1) / TILE), (unsigned)bhq);
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
   cudaError_t e;
   switch (key) {

@@ -1,10 +1,10 @@
 // extern "C" boundary of libsage_b200.so (declared in include/sage_b200.h): argument checks,
-// workspace carving and the two launches.  Nothing here allocates or synchronises.
+// workspace carving and the launches.  Nothing here allocates or synchronises.
 #include <stdarg.h>
-
-#include <mutex>
 #include <stdio.h>
 #include <string.h>
+
+#include <mutex>
 
 #include "../../include/sage_b200.h"
 #include "sage_common.cuh"
@@ -68,43 +68,149 @@ int check_strides(const char* name, const int64_t s[3]) {
   return SAGE_OK;
 }
 
-int check_dims(int64_t B, int64_t H, int64_t N) {
-  if (B < 1 || H < 1 || N < 1) return fail(SAGE_E_ARG, "B, H and N must be >= 1 (got %lld, %lld, %lld)",
-                                            (long long)B, (long long)H, (long long)N);
-  if (B * H > 65535) return fail(SAGE_E_UNSUPPORTED, "B*H = %lld exceeds the grid limit 65535", (long long)(B * H));
-  if (N > (int64_t)1 << 30) return fail(SAGE_E_UNSUPPORTED, "N = %lld exceeds 2^30", (long long)N);
+// Shape of one call: B batches; Hq query heads sharing Hkv key/value heads (Hq a multiple of Hkv);
+// Nq query rows; Nk keys.
+struct Dims {
+  int64_t B, Hq, Hkv, Nq, Nk;
+};
+
+int check_dims(const Dims& d) {
+  if (d.B < 1 || d.Hq < 1 || d.Hkv < 1 || d.Nq < 1 || d.Nk < 1)
+    return fail(SAGE_E_ARG, "B, heads and lengths must be >= 1 (got B=%lld Hq=%lld Hkv=%lld Nq=%lld Nk=%lld)",
+                (long long)d.B, (long long)d.Hq, (long long)d.Hkv, (long long)d.Nq, (long long)d.Nk);
+  if (d.Hq % d.Hkv) return fail(SAGE_E_ARG, "query heads (%lld) must be a multiple of key/value heads (%lld)",
+                                (long long)d.Hq, (long long)d.Hkv);
+  if (d.B * d.Hq > 65535) return fail(SAGE_E_UNSUPPORTED, "B*H = %lld exceeds the grid limit 65535", (long long)(d.B * d.Hq));
+  if (d.Nq > (int64_t)1 << 30 || d.Nk > (int64_t)1 << 30) return fail(SAGE_E_UNSUPPORTED, "sequence length exceeds 2^30");
   return SAGE_OK;
 }
 
 struct Layout {
-  size_t q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status, total;
+  size_t q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status, qm, total;
 };
 
-Layout carve(int64_t B, int64_t H, int64_t N) {
-  const size_t bh = (size_t)(B * H), n = (size_t)N, np = (size_t)sage_pad_len(N);
+Layout carve(const Dims& d) {
+  const size_t bhq = (size_t)(d.B * d.Hq), bhk = (size_t)(d.B * d.Hkv);
+  const size_t nq = (size_t)d.Nq, np = (size_t)sage_pad_len(d.Nk);
   Layout L;
   size_t off = 0;
   auto take = [&](size_t bytes) { size_t o = off; off = align256(off + bytes); return o; };
-  L.q8 = take(bh * n * sage::HD);
-  L.sq = take(bh * n * 4);
-  L.k8 = take(bh * np * sage::HD);
-  L.sk = take(bh * np * 4);
-  L.v8t = take(bh * np * sage::HD);
-  L.sv = take(bh * np * 4);
-  L.svp = take(bh * np * 4);
-  L.s_fold = take(bh * 4);
-  L.mean = take(bh * sage::HD * 4);
-  L.ctrl = take(sage::prologue_ctrl_bytes(B, H, N));
+  L.q8 = take(bhq * nq * sage::HD);
+  L.sq = take(bhq * nq * 4);
+  L.k8 = take(bhk * np * sage::HD);
+  L.sk = take(bhk * np * 4);
+  L.v8t = take(bhk * np * sage::HD);
+  L.sv = take(bhk * np * 4);
+  L.svp = take(bhk * np * 4);
+  L.s_fold = take(bhk * 4);
+  L.mean = take(bhk * sage::HD * 4);
+  L.ctrl = take(sage::prologue_ctrl_bytes(d.B, d.Hkv, d.Nk));
   L.status = take(256);
+  L.qm = take(bhq * nq * 4);
   L.total = off;
   return L;
+}
+
+int prologue_impl(const void* q, const void* k, const void* v,
+                  void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
+                  float* s_fold, float* mean, float* qm, void* ctrl, const Dims& d, int64_t Nk_pad,
+                  const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                  int dtype, int qk_mode, int smooth_k, void* stream, const char* who) {
+  g_err[0] = 0;
+  int rc = check_dims(d);
+  if (rc) return rc;
+  if (!q || !k || !v || !q8 || !sq || !k8 || !sk || !v8t || !sv || !svp || !s_fold || !ctrl)
+    return fail(SAGE_E_ARG, "%s: null pointer argument", who);
+  if (smooth_k && !mean) return fail(SAGE_E_ARG, "%s: smooth_k needs a mean buffer", who);
+  if (qm && !smooth_k) return fail(SAGE_E_ARG, "%s: the q.mean output only exists with smooth_k", who);
+  if (Nk_pad != sage_pad_len(d.Nk)) return fail(SAGE_E_ARG, "%s: padded key length must be %lld", who, (long long)sage_pad_len(d.Nk));
+  if (dtype != SAGE_F16 && dtype != SAGE_BF16) return fail(SAGE_E_ARG, "%s: dtype must be SAGE_F16 or SAGE_BF16", who);
+  if (qk_mode != SAGE_QK_INT8 && qk_mode != SAGE_QK_E4M3) return fail(SAGE_E_ARG, "%s: bad qk_mode", who);
+  if ((rc = check_strides("q", q_strides)) || (rc = check_strides("k", k_strides)) || (rc = check_strides("v", v_strides)))
+    return rc;
+  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(q8) || !aligned16(k8) || !aligned16(v8t) ||
+      !aligned16(sk) || !aligned16(svp) || !aligned16(ctrl))
+    return fail(SAGE_E_ARG, "%s: pointers must be 16-byte aligned", who);
+  sage::PrologueParams p;
+  p.q = q; p.k = k; p.v = v; p.q8 = q8; p.k8 = k8; p.v8t = v8t;
+  p.sq = sq; p.sk = sk; p.sv = sv; p.svp = svp; p.s_fold = s_fold; p.mean = mean; p.ctrl = ctrl; p.qm = qm;
+  p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq;
+  for (int i = 0; i < 3; ++i) { p.q_strides[i] = q_strides[i]; p.k_strides[i] = k_strides[i]; p.v_strides[i] = v_strides[i]; }
+  p.dtype = dtype; p.qk_mode = qk_mode; p.smooth_k = smooth_k;
+  cudaError_t e = sage::launch_prologue(p, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s", who, cudaGetErrorString(e));
+  return SAGE_OK;
+}
+
+int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
+              const void* v8t, const float* svp, const float* s_fold, void* out, float* lse, const float* qm,
+              const Dims& d, int64_t Nk_pad, const int64_t o_strides[3],
+              int causal, float sm_scale, int out_dtype, int qk_mode, int32_t* status, void* stream,
+              const char* who) {
+  g_err[0] = 0;
+  int rc = check_dims(d);
+  if (rc) return rc;
+  if (!q8 || !sq || !k8 || !sk || !v8t || !svp || !s_fold || !out || !status)
+    return fail(SAGE_E_ARG, "%s: null pointer argument", who);
+  if (Nk_pad != sage_pad_len(d.Nk)) return fail(SAGE_E_ARG, "%s: padded key length must be %lld", who, (long long)sage_pad_len(d.Nk));
+  if (causal && d.Nq != d.Nk) return fail(SAGE_E_ARG, "%s: a causal call needs as many queries as keys", who);
+  if (out_dtype != SAGE_F16 && out_dtype != SAGE_BF16) return fail(SAGE_E_ARG, "%s: bad out_dtype", who);
+  if (qk_mode != SAGE_QK_INT8 && qk_mode != SAGE_QK_E4M3) return fail(SAGE_E_ARG, "%s: bad qk_mode", who);
+  if ((rc = check_strides("out", o_strides))) return rc;
+  if (!aligned16(q8) || !aligned16(k8) || !aligned16(v8t) || !aligned16(sk) || !aligned16(svp) || !aligned16(out))
+    return fail(SAGE_E_ARG, "%s: pointers must be 16-byte aligned", who);
+  if (!(sm_scale == sm_scale)) return fail(SAGE_E_ARG, "%s: sm_scale is NaN", who);
+  sage::AttnParams p;
+  p.q8 = q8; p.k8 = k8; p.v8t = v8t; p.sq = sq; p.sk = sk; p.svp = svp; p.s_fold = s_fold; p.out = out;
+  p.lse = lse; p.qm = qm;
+  p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq;
+  for (int i = 0; i < 3; ++i) p.o_strides[i] = o_strides[i];
+  p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.out_dtype = out_dtype; p.qk_mode = qk_mode;
+  p.status = status;
+  const char* why = nullptr;
+  cudaError_t e = sage::launch_attention(p, reinterpret_cast<cudaStream_t>(stream), &why);
+  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s (%s)", who, why ? why : "", cudaGetErrorString(e));
+  return SAGE_OK;
+}
+
+int attention_impl(const void* q, const void* k, const void* v, void* out, float* lse,
+                   void* workspace, size_t workspace_bytes, const Dims& d,
+                   const int64_t q_strides[3], const int64_t k_strides[3],
+                   const int64_t v_strides[3], const int64_t o_strides[3],
+                   int dtype, int qk_mode, int causal, int smooth_k, float sm_scale, void* stream,
+                   const char* who) {
+  g_err[0] = 0;
+  int rc = check_dims(d);
+  if (rc) return rc;
+  if (!workspace) return fail(SAGE_E_ARG, "%s: workspace is null", who);
+  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(SAGE_E_ARG, "%s: workspace must be 256-byte aligned", who);
+  const Layout L = carve(d);
+  if (workspace_bytes < L.total)
+    return fail(SAGE_E_WORKSPACE, "%s: workspace has %zu bytes, needs %zu", who, workspace_bytes, L.total);
+  if (qk_mode < 0) qk_mode = (dtype == SAGE_BF16) ? SAGE_QK_E4M3 : SAGE_QK_INT8;
+  char* w = reinterpret_cast<char*>(workspace);
+  const int64_t Nk_pad = sage_pad_len(d.Nk);
+  int32_t* status = reinterpret_cast<int32_t*>(w + L.status);
+  cudaError_t e = cudaMemsetAsync(status, 0, 4, reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s", who, cudaGetErrorString(e));
+  float* qm = (lse && smooth_k) ? reinterpret_cast<float*>(w + L.qm) : nullptr;
+  rc = prologue_impl(q, k, v, w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
+                     reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.sv),
+                     reinterpret_cast<float*>(w + L.svp), reinterpret_cast<float*>(w + L.s_fold),
+                     reinterpret_cast<float*>(w + L.mean), qm, w + L.ctrl, d, Nk_pad,
+                     q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, who);
+  if (rc) return rc;
+  return attn_impl(w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
+                   reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.svp),
+                   reinterpret_cast<float*>(w + L.s_fold), out, lse, qm, d, Nk_pad, o_strides,
+                   causal, sm_scale, dtype, qk_mode, status, stream, who);
 }
 
 }  // namespace
 
 extern "C" {
 
-int sage_version(void) { return 100; }
+int sage_version(void) { return 200; }
 
 const char* sage_last_error(void) { return g_err; }
 
@@ -121,29 +227,20 @@ int sage_prologue(const void* q, const void* k, const void* v,
                   int64_t B, int64_t H, int64_t N, int64_t N_pad,
                   const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                   int dtype, int qk_mode, int smooth_k, void* stream) {
-  g_err[0] = 0;
-  int rc = check_dims(B, H, N);
-  if (rc) return rc;
-  if (!q || !k || !v || !q8 || !sq || !k8 || !sk || !v8t || !sv || !svp || !s_fold || !ctrl)
-    return fail(SAGE_E_ARG, "sage_prologue: null pointer argument");
-  if (smooth_k && !mean) return fail(SAGE_E_ARG, "sage_prologue: smooth_k needs a mean buffer");
-  if (N_pad != sage_pad_len(N)) return fail(SAGE_E_ARG, "sage_prologue: N_pad must be %lld", (long long)sage_pad_len(N));
-  if (dtype != SAGE_F16 && dtype != SAGE_BF16) return fail(SAGE_E_ARG, "sage_prologue: dtype must be SAGE_F16 or SAGE_BF16");
-  if (qk_mode != SAGE_QK_INT8 && qk_mode != SAGE_QK_E4M3) return fail(SAGE_E_ARG, "sage_prologue: bad qk_mode");
-  if ((rc = check_strides("q", q_strides)) || (rc = check_strides("k", k_strides)) || (rc = check_strides("v", v_strides)))
-    return rc;
-  if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(q8) || !aligned16(k8) || !aligned16(v8t) ||
-      !aligned16(sk) || !aligned16(svp) || !aligned16(ctrl))
-    return fail(SAGE_E_ARG, "sage_prologue: pointers must be 16-byte aligned");
-  sage::PrologueParams p;
-  p.q = q; p.k = k; p.v = v; p.q8 = q8; p.k8 = k8; p.v8t = v8t;
-  p.sq = sq; p.sk = sk; p.sv = sv; p.svp = svp; p.s_fold = s_fold; p.mean = mean; p.ctrl = ctrl;
-  p.B = B; p.H = H; p.N = N; p.N_pad = N_pad;
-  for (int i = 0; i < 3; ++i) { p.q_strides[i] = q_strides[i]; p.k_strides[i] = k_strides[i]; p.v_strides[i] = v_strides[i]; }
-  p.dtype = dtype; p.qk_mode = qk_mode; p.smooth_k = smooth_k;
-  cudaError_t e = sage::launch_prologue(p, reinterpret_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "sage_prologue: %s", cudaGetErrorString(e));
-  return SAGE_OK;
+  const Dims d = {B, H, H, N, N};
+  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, nullptr, ctrl, d, N_pad,
+                       q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, "sage_prologue");
+}
+
+int sage_prologue_ex(const void* q, const void* k, const void* v,
+                     void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
+                     float* s_fold, float* mean, float* qm, void* ctrl,
+                     int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad,
+                     const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
+                     int dtype, int qk_mode, int smooth_k, void* stream) {
+  const Dims d = {B, Hq, Hkv, Nq, Nk};
+  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, qm, ctrl, d, Nk_pad,
+                       q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, "sage_prologue_ex");
 }
 
 size_t sage_prologue_static_ctrl_capacity(void) { return kStaticCtrlBytes; }
@@ -156,7 +253,8 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
                               const int64_t v_strides[3],
                               int dtype, int qk_mode, int smooth_k, void* stream) {
   g_err[0] = 0;
-  int rc = check_dims(B, H, N);
+  const Dims d = {B, H, H, N, N};
+  int rc = check_dims(d);
   if (rc) return rc;
   const size_t need = sage::prologue_ctrl_bytes(B, H, N);
   if (need > kStaticCtrlBytes)
@@ -166,8 +264,9 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
   void* ctrl = nullptr;
   rc = static_ctrl_address(&ctrl);
   if (rc) return rc;
-  return sage_prologue(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, B, H, N, N_pad,
-                       q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream);
+  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, nullptr, ctrl, d, N_pad,
+                       q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream,
+                       "sage_prologue_static_ctrl");
 }
 
 int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* sk,
@@ -175,43 +274,54 @@ int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* 
                   int64_t B, int64_t H, int64_t N, int64_t N_pad, const int64_t o_strides[3],
                   int causal, float sm_scale, int out_dtype, int qk_mode,
                   int32_t* status, void* stream) {
-  g_err[0] = 0;
-  int rc = check_dims(B, H, N);
-  if (rc) return rc;
-  if (!q8 || !sq || !k8 || !sk || !v8t || !svp || !s_fold || !out || !status)
-    return fail(SAGE_E_ARG, "sage_attn_fwd: null pointer argument");
-  if (N_pad != sage_pad_len(N)) return fail(SAGE_E_ARG, "sage_attn_fwd: N_pad must be %lld", (long long)sage_pad_len(N));
-  if (out_dtype != SAGE_F16 && out_dtype != SAGE_BF16) return fail(SAGE_E_ARG, "sage_attn_fwd: bad out_dtype");
-  if (qk_mode != SAGE_QK_INT8 && qk_mode != SAGE_QK_E4M3) return fail(SAGE_E_ARG, "sage_attn_fwd: bad qk_mode");
-  if ((rc = check_strides("out", o_strides))) return rc;
-  if (!aligned16(q8) || !aligned16(k8) || !aligned16(v8t) || !aligned16(sk) || !aligned16(svp) || !aligned16(out))
-    return fail(SAGE_E_ARG, "sage_attn_fwd: pointers must be 16-byte aligned");
-  if (!(sm_scale == sm_scale)) return fail(SAGE_E_ARG, "sage_attn_fwd: sm_scale is NaN");
-  sage::AttnParams p;
-  p.q8 = q8; p.k8 = k8; p.v8t = v8t; p.sq = sq; p.sk = sk; p.svp = svp; p.s_fold = s_fold; p.out = out;
-  p.B = B; p.H = H; p.N = N; p.N_pad = N_pad;
-  for (int i = 0; i < 3; ++i) p.o_strides[i] = o_strides[i];
-  p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.out_dtype = out_dtype; p.qk_mode = qk_mode;
-  p.status = status;
-  const char* why = nullptr;
-  cudaError_t e = sage::launch_attention(p, reinterpret_cast<cudaStream_t>(stream), &why);
-  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "sage_attn_fwd: %s (%s)", why ? why : "", cudaGetErrorString(e));
-  return SAGE_OK;
+  const Dims d = {B, H, H, N, N};
+  return attn_impl(q8, sq, k8, sk, v8t, svp, s_fold, out, nullptr, nullptr, d, N_pad, o_strides,
+                   causal, sm_scale, out_dtype, qk_mode, status, stream, "sage_attn_fwd");
+}
+
+int sage_attn_fwd_ex(const void* q8, const float* sq, const void* k8, const float* sk,
+                     const void* v8t, const float* svp, const float* s_fold, void* out,
+                     float* lse, const float* qm,
+                     int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad,
+                     const int64_t o_strides[3], int causal, float sm_scale, int out_dtype, int qk_mode,
+                     int32_t* status, void* stream) {
+  const Dims d = {B, Hq, Hkv, Nq, Nk};
+  return attn_impl(q8, sq, k8, sk, v8t, svp, s_fold, out, lse, qm, d, Nk_pad, o_strides,
+                   causal, sm_scale, out_dtype, qk_mode, status, stream, "sage_attn_fwd_ex");
 }
 
 void sage_debug_score_dump(void* ptr, int key_tile) { sage::set_score_dump(ptr, key_tile); }
 
 size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N) {
   if (B < 1 || H < 1 || N < 1) return 0;
-  return carve(B, H, N).total;
+  const Dims d = {B, H, H, N, N};
+  return carve(d).total;
+}
+
+size_t sage_workspace_bytes_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk) {
+  const Dims d = {B, Hq, Hkv, Nq, Nk};
+  if (B < 1 || Hq < 1 || Hkv < 1 || Nq < 1 || Nk < 1 || Hq % Hkv) return 0;
+  return carve(d).total;
+}
+
+static int layout_out(const Dims& d, size_t* offsets, int n) {
+  const Layout L = carve(d);
+  const size_t o[12] = {L.q8, L.sq, L.k8, L.sk, L.v8t, L.sv, L.svp, L.s_fold, L.mean, L.ctrl, L.status, L.qm};
+  memcpy(offsets, o, sizeof(size_t) * (size_t)n);
+  return n;
 }
 
 int sage_workspace_layout(int64_t B, int64_t H, int64_t N, size_t offsets[11]) {
   if (B < 1 || H < 1 || N < 1 || !offsets) return fail(SAGE_E_ARG, "sage_workspace_layout: bad argument");
-  const Layout L = carve(B, H, N);
-  const size_t o[11] = {L.q8, L.sq, L.k8, L.sk, L.v8t, L.sv, L.svp, L.s_fold, L.mean, L.ctrl, L.status};
-  memcpy(offsets, o, sizeof(o));
-  return 11;
+  const Dims d = {B, H, H, N, N};
+  return layout_out(d, offsets, 11);
+}
+
+int sage_workspace_layout_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, size_t offsets[12]) {
+  if (B < 1 || Hq < 1 || Hkv < 1 || Nq < 1 || Nk < 1 || Hq % Hkv || !offsets)
+    return fail(SAGE_E_ARG, "sage_workspace_layout_ex: bad argument");
+  const Dims d = {B, Hq, Hkv, Nq, Nk};
+  return layout_out(d, offsets, 12);
 }
 
 int sage_attention(const void* q, const void* k, const void* v, void* out,
@@ -220,30 +330,20 @@ int sage_attention(const void* q, const void* k, const void* v, void* out,
                    const int64_t q_strides[3], const int64_t k_strides[3],
                    const int64_t v_strides[3], const int64_t o_strides[3],
                    int dtype, int qk_mode, int causal, int smooth_k, float sm_scale, void* stream) {
-  g_err[0] = 0;
-  int rc = check_dims(B, H, N);
-  if (rc) return rc;
-  if (!workspace) return fail(SAGE_E_ARG, "sage_attention: workspace is null");
-  if (reinterpret_cast<uintptr_t>(workspace) & 255u) return fail(SAGE_E_ARG, "sage_attention: workspace must be 256-byte aligned");
-  const Layout L = carve(B, H, N);
-  if (workspace_bytes < L.total)
-    return fail(SAGE_E_WORKSPACE, "sage_attention: workspace has %zu bytes, needs %zu", workspace_bytes, L.total);
-  if (qk_mode < 0) qk_mode = (dtype == SAGE_BF16) ? SAGE_QK_E4M3 : SAGE_QK_INT8;
-  char* w = reinterpret_cast<char*>(workspace);
-  const int64_t N_pad = sage_pad_len(N);
-  int32_t* status = reinterpret_cast<int32_t*>(w + L.status);
-  cudaError_t e = cudaMemsetAsync(status, 0, 4, reinterpret_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "sage_attention: %s", cudaGetErrorString(e));
-  rc = sage_prologue(q, k, v, w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
-                     reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.sv),
-                     reinterpret_cast<float*>(w + L.svp), reinterpret_cast<float*>(w + L.s_fold),
-                     reinterpret_cast<float*>(w + L.mean), w + L.ctrl, B, H, N, N_pad,
-                     q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream);
-  if (rc) return rc;
-  return sage_attn_fwd(w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
-                       reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.svp),
-                       reinterpret_cast<float*>(w + L.s_fold), out, B, H, N, N_pad, o_strides,
-                       causal, sm_scale, dtype, qk_mode, status, stream);
+  const Dims d = {B, H, H, N, N};
+  return attention_impl(q, k, v, out, nullptr, workspace, workspace_bytes, d, q_strides, k_strides, v_strides,
+                        o_strides, dtype, qk_mode, causal, smooth_k, sm_scale, stream, "sage_attention");
+}
+
+int sage_attention_ex(const void* q, const void* k, const void* v, void* out, float* lse,
+                      void* workspace, size_t workspace_bytes,
+                      int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk,
+                      const int64_t q_strides[3], const int64_t k_strides[3],
+                      const int64_t v_strides[3], const int64_t o_strides[3],
+                      int dtype, int qk_mode, int causal, int smooth_k, float sm_scale, void* stream) {
+  const Dims d = {B, Hq, Hkv, Nq, Nk};
+  return attention_impl(q, k, v, out, lse, workspace, workspace_bytes, d, q_strides, k_strides, v_strides,
+                        o_strides, dtype, qk_mode, causal, smooth_k, sm_scale, stream, "sage_attention_ex");
 }
 
 }  // extern "C"

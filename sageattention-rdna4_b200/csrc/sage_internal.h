@@ -11,7 +11,9 @@ struct PrologueParams {
   void *q8, *k8, *v8t;
   float *sq, *sk, *sv, *svp, *s_fold, *mean;
   void* ctrl;
-  int64_t B, H, N, N_pad;
+  float* qm;                                           // optional (B*Hq, Nq): q . K-mean, for the LSE
+  int64_t B, H, N, N_pad;                              // K/V side: heads, keys, padded keys
+  int64_t Hq, Nq;                                      // query side (Hq a multiple of H)
   int64_t q_strides[3], k_strides[3], v_strides[3];   // (batch, head, row) in elements
   int dtype;      // 0 fp16, 1 bf16
   int qk_mode;    // 0 int8, 1 e4m3
@@ -22,7 +24,10 @@ struct AttnParams {
   const void *q8, *k8, *v8t;
   const float *sq, *sk, *svp, *s_fold;
   void* out;
-  int64_t B, H, N, N_pad;
+  float* lse;                                          // optional (B*Hq, Nq) natural-log sum of exponentials
+  const float* qm;                                     // with lse and smooth_k: q . K-mean per query row
+  int64_t B, H, N, N_pad;                              // K/V side: heads, keys, padded keys
+  int64_t Hq, Nq;                                      // query side
   int64_t o_strides[3];                                // (batch, head, row) in elements
   int causal;
   float sm_scale;

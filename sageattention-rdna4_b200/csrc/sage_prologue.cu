@@ -94,7 +94,10 @@ struct QuantArgs {
   float *sq, *sk, *sv, *svp, *s_fold;
   const float* mean;
   unsigned *arrivals, *svmax_bits;
-  long long N, N_pad, H;
+  long long N, N_pad, H;          // keys: length, padded length, K/V heads per batch element
+  long long Nq, Hq, group;        // queries: length, heads per batch element, Hq / H (1 without GQA)
+  long long BHq, BHkv;            // B*Hq, B*H
+  float* qm;                      // optional (B*Hq, Nq): dot(q row, K mean of its K/V head), for the LSE
   long long q_sb, q_sh, q_sr, k_sb, k_sh, k_sr, v_sb, v_sh, v_sr;
   int sub_mean;
 };
@@ -141,16 +144,22 @@ quant_qkv_kernel(const QuantArgs a) {
   const int tid = threadIdx.x, c = tid & 15, r0 = tid >> 4, lane = tid & 31, warp = tid >> 5;
   const int bh = gridDim.y - 1 - blockIdx.y;         // last heads first: their K is still in L2 after the mean pass
   const int which = blockIdx.z == 0 ? 1 : (blockIdx.z == 1 ? 0 : 2);   // 0 Q, 1 K, 2 V; K tiles are issued first
-  const long long b = bh / a.H, h = bh - b * a.H;
   const long long n_base = (long long)blockIdx.x * TILE;
-  const long long N = a.N, N_pad = a.N_pad;
   uint4 raw[8];
 
   if (which == 0) {
     // ---------------------------------- Q ----------------------------------
-    if (n_base >= N) return;
+    const long long N = a.Nq;
+    if (bh >= a.BHq || n_base >= N) return;
+    const long long b = bh / a.Hq, h = bh - b * a.Hq;
     const T* qb = reinterpret_cast<const T*>(a.q) + b * a.q_sb + h * a.q_sh + 8 * c;
     load_rows<T>(qb, a.q_sr, n_base, r0, N, raw);
+    float mu[8];
+    if (a.qm != nullptr) {                            // the K mean of this query head's K/V head
+      const long long bh_kv = b * a.H + h / a.group;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) mu[e] = a.mean[(size_t)bh_kv * HD + 8 * c + e];
+    }
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const long long n = n_base + r0 + 16 * i;
@@ -178,9 +187,23 @@ quant_qkv_kernel(const QuantArgs a) {
         *reinterpret_cast<uint2*>(a.q8 + ((size_t)bh * N + n) * HD + 8 * c) = w;
         if (c == 0) a.sq[(size_t)bh * N + n] = __fdiv_rn(amax, QMAX);
       }
+      if (a.qm != nullptr) {                          // fixed-order fp32 dot product of the raw row
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) d = __fmaf_rn(x[e], mu[e], d);
+        d += __shfl_xor_sync(0xffffffffu, d, 8);
+        d += __shfl_xor_sync(0xffffffffu, d, 4);
+        d += __shfl_xor_sync(0xffffffffu, d, 2);
+        d += __shfl_xor_sync(0xffffffffu, d, 1);
+        if (c == 0 && n < N) a.qm[(size_t)bh * N + n] = d;
+      }
     }
     return;
   }
+
+  const long long N = a.N, N_pad = a.N_pad;
+  if (bh >= a.BHkv || n_base >= N_pad) return;
+  const long long b = bh / a.H, h = bh - b * a.H;
 
   if (which == 1) {
     // ---------------------------------- K ----------------------------------
@@ -297,7 +320,7 @@ quant_qkv_kernel(const QuantArgs a) {
     for (int w = 1; w < 8; ++w) m = fmaxf(m, s_wmax[w]);
     atomicMax(&a.svmax_bits[bh], __float_as_uint(m));
     __threadfence();
-    s_last = (atomicAdd(&a.arrivals[bh], 1u) == gridDim.x - 1);
+    s_last = (atomicAdd(&a.arrivals[bh], 1u) == (unsigned)(N_pad / TILE) - 1u);
   }
   __syncthreads();
   if (s_last) {
@@ -339,11 +362,13 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   a.sq = p.sq; a.sk = p.sk; a.sv = p.sv; a.svp = p.svp; a.s_fold = p.s_fold; a.mean = p.mean;
   a.arrivals = words + bh; a.svmax_bits = words + 2 * bh;
   a.N = p.N; a.N_pad = p.N_pad; a.H = p.H;
+  a.Nq = p.Nq; a.Hq = p.Hq; a.group = p.Hq / p.H; a.BHq = p.B * p.Hq; a.BHkv = bh; a.qm = p.qm;
   a.q_sb = p.q_strides[0]; a.q_sh = p.q_strides[1]; a.q_sr = p.q_strides[2];
   a.k_sb = p.k_strides[0]; a.k_sh = p.k_strides[1]; a.k_sr = p.k_strides[2];
   a.v_sb = p.v_strides[0]; a.v_sh = p.v_strides[1]; a.v_sr = p.v_strides[2];
   a.sub_mean = p.smooth_k ? 1 : 0;
-  dim3 grid((unsigned)(p.N_pad / TILE), (unsigned)bh, 3);
+  const int64_t tq = (p.Nq + TILE - 1) / TILE, tk = p.N_pad / TILE;
+  dim3 grid((unsigned)(tq > tk ? tq : tk), (unsigned)(a.BHq > bh ? a.BHq : bh), 3);
   if (p.qk_mode == 0) quant_qkv_kernel<T, true><<<grid, 256, 0, st>>>(a);
   else quant_qkv_kernel<T, false><<<grid, 256, 0, st>>>(a);
   return cudaGetLastError();

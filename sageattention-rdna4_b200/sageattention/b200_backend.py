@@ -65,12 +65,13 @@ def strided_view_reason(t: torch.Tensor) -> Optional[str]:
 def envelope_reason(q, k, v, tensor_layout, return_lse=False, smooth_v=False, attn_mask=None,
                     require_cuda=True) -> Optional[str]:
     """None if the call is inside the envelope, else a short reason (the reference's strings:
-    layout, return_lse, attn_mask, smooth_v, device, dtype, rank, stride_*, ptr_align, head_dim,
-    batch, heads, seq_len).  head_dim 64 is refused here (the reference falls back for it)."""
+    layout, attn_mask, smooth_v, device, dtype, rank, stride_*, ptr_align, head_dim, batch, heads,
+    seq_len).  head_dim 64 is refused here (the reference falls back for it).  Wider than the
+    reference's hand-written path in three places, following the upstream contract
+    (sageattention/core.py:1081-1101): `return_lse` is served, the query heads may be a multiple of
+    the key/value heads, and the key length may differ from the query length."""
     if tensor_layout not in ("HND", "NHD"):
         return "layout"
-    if return_lse:
-        return "return_lse"
     if attn_mask is not None:
         return "attn_mask"
     if smooth_v:
@@ -95,11 +96,11 @@ def envelope_reason(q, k, v, tensor_layout, return_lse=False, smooth_v=False, at
         return "head_dim"
     if q.size(0) != k.size(0) or q.size(0) != v.size(0):
         return "batch"
-    if q.size(1) != k.size(1) or q.size(1) != v.size(1):
+    if k.size(1) != v.size(1) or k.size(1) < 1 or q.size(1) % k.size(1):
         return "heads"
-    if q.size(2) != k.size(2) or k.size(2) != v.size(2):
+    if k.size(2) != v.size(2):
         return "seq_len"
-    if q.size(2) < 1:
+    if q.size(2) < 1 or k.size(2) < 1:
         return "seq_len"
     return None
 
@@ -201,16 +202,19 @@ _ws_cache: "OrderedDict[Tuple, torch.Tensor]" = OrderedDict()
 _WS_CACHE_ENTRIES = 4
 
 
-def _workspace(dev, stream_id: int, b: int, h: int, n: int) -> torch.Tensor:
+def _workspace(dev, stream_id: int, b: int, h: int, n: int, hkv: Optional[int] = None,
+               nk: Optional[int] = None) -> torch.Tensor:
     """A cached workspace per (device, stream, shape): intermediates of one call live only until
     the attention kernel of that call has run, and calls on one stream are ordered."""
-    key = (dev.index, stream_id, b, h, n)
+    hkv = h if hkv is None else hkv
+    nk = n if nk is None else nk
+    key = (dev.index, stream_id, b, h, hkv, n, nk)
     with _ws_lock:
         ws = _ws_cache.get(key)
         if ws is not None:
             _ws_cache.move_to_end(key)
             return ws
-    nbytes = _native.load().sage_workspace_bytes(b, h, n)
+    nbytes = _native.load().sage_workspace_bytes_ex(b, h, hkv, n, nk)
     ws = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
     with _ws_lock:
         _ws_cache[key] = ws
@@ -225,9 +229,10 @@ def clear_workspaces():
 
 
 def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=True,
-              int8: Optional[bool] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Prologue + attention through the single C entry point `sage_attention`.  Returns a tensor
-    with q's shape, dtype and layout.  Raises ValueError for a call outside the envelope."""
+              int8: Optional[bool] = None, out: Optional[torch.Tensor] = None, return_lse: bool = False):
+    """Prologue + attention through the single C entry point `sage_attention_ex`.  Returns a tensor
+    with q's shape, dtype and layout -- and, with `return_lse`, also the fp32 log-sum-exp
+    (B, Hq, Nq).  Raises ValueError for a call outside the envelope."""
     reason = envelope_reason(q, k, v, tensor_layout)
     with _counters_lock:
         _counters["calls"] += 1
@@ -245,6 +250,9 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     else:
         ql, kl, vl = q, k, v
     b, h, n, d = ql.shape
+    hkv, nk = int(kl.shape[1]), int(kl.shape[2])
+    if is_causal and nk != n:
+        raise ValueError("sageattn (B200 path): a causal call needs q_len == kv_len")
     dev = q.device
     if sm_scale is None:
         sm_scale = d ** -0.5
@@ -258,14 +266,17 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     else:
         qk_mode = _native.SAGE_QK_INT8 if int8 else _native.SAGE_QK_E4M3
     stream = torch.cuda.current_stream(dev)
-    ws = _workspace(dev, int(stream.cuda_stream), b, h, n)
+    ws = _workspace(dev, int(stream.cuda_stream), b, h, n, hkv, nk)
+    lse = torch.empty((b, h, n), dtype=torch.float32, device=dev) if return_lse else None
     with torch.cuda.device(dev):
-        rc = lib.sage_attention(
-            _ptr(ql), _ptr(kl), _ptr(vl), _ptr(ol), _ptr(ws), ws.numel(), b, h, n,
+        rc = lib.sage_attention_ex(
+            _ptr(ql), _ptr(kl), _ptr(vl), _ptr(ol), _ptr(lse), _ptr(ws), ws.numel(), b, h, hkv, n, nk,
             _bhr(ql), _bhr(kl), _bhr(vl), _bhr(ol), _dtype_code(q.dtype), qk_mode,
             1 if is_causal else 0, 1 if smooth_k else 0, float(sm_scale),
             ctypes.c_void_p(int(stream.cuda_stream)))
-    _native.check(rc, "sage_attention")
+    _native.check(rc, "sage_attention_ex")
+    if return_lse:
+        return out, lse
     return out
 
 
@@ -293,11 +304,16 @@ def workspace_views(b: int, h: int, n: int, ws: torch.Tensor, int8: bool) -> Dic
         status=seg(10, 4).view(torch.int32))
 
 
-def last_status(q_like: torch.Tensor, b: int, h: int, n: int) -> int:
+def last_status(q_like: torch.Tensor, b: int, h: int, n: int, hkv: Optional[int] = None,
+                nk: Optional[int] = None) -> int:
     """Status word of the most recent call of that shape on the current stream (synchronises)."""
     dev = q_like.device
-    ws = _workspace(dev, int(torch.cuda.current_stream(dev).cuda_stream), b, h, n)
-    return int(workspace_views(b, h, n, ws, True)["status"].item())
+    ws = _workspace(dev, int(torch.cuda.current_stream(dev).cuda_stream), b, h, n, hkv, nk)
+    lib = _native.load()
+    offs = (ctypes.c_size_t * 12)()
+    if lib.sage_workspace_layout_ex(b, h, h if hkv is None else hkv, n, n if nk is None else nk, offs) != 12:
+        raise _native.SageNativeError("sage_workspace_layout_ex failed")
+    return int(ws[offs[10]: offs[10] + 4].view(torch.int32).item())
 
 
 def status() -> dict:

@@ -21,8 +21,6 @@ def _reject_common(return_lse: bool, kwargs: dict):
         raise NotImplementedError(
             "sageattention (B200 path) does not implement attn_mask; refusing to ignore it. "
             "Pass mask=None or use a backend that supports masking.")
-    if return_lse:
-        raise NotImplementedError("sageattention (B200 path) does not implement return_lse")
     if kwargs.get("smooth_v", False):
         raise NotImplementedError("sageattention (B200 path) does not implement smooth_v")
 
@@ -42,9 +40,12 @@ def sageattn(
 ) -> torch.Tensor:
     """Quantised attention: per-token int8 Q.K (e4m3 for bf16 inputs), e4m3 P.V, fp32 softmax.
 
-    q, k, v : ``[B, H, N, 128]`` (``tensor_layout="HND"``) or ``[B, N, H, 128]`` (``"NHD"``),
-        float16 or bfloat16, same shape, on one CUDA device; strided views are accepted when the
-        last axis is contiguous and every other stride is a multiple of 8 elements.
+    q : ``[B, Hq, Nq, 128]`` (``tensor_layout="HND"``) or ``[B, Nq, Hq, 128]`` (``"NHD"``);
+    k, v : the same with ``Hkv`` heads and ``Nk`` rows; ``Hq`` a multiple of ``Hkv`` (grouped-query
+        attention), ``Nk`` may differ from ``Nq`` when the call is not causal.  float16 or
+        bfloat16, one CUDA device; strided views are accepted when the last axis is contiguous and
+        every other stride is a multiple of 8 elements.
+    return_lse : also return the fp32 log-sum-exp ``[B, Hq, Nq]`` of ``sm_scale * q.k``.
     is_causal : causal mask (query i sees keys <= i).
     sm_scale : softmax scale, default ``128 ** -0.5``.
     smooth_k (kwarg, default True) : subtract the per-channel sequence mean of K before
@@ -53,7 +54,7 @@ def sageattn(
         default (int8 for float16).  bfloat16 inputs always use e4m3 codes.
     sk1_backend, sk1_bf16 : accepted for call compatibility; ``False`` asks for a path this
         package does not have and raises.
-    Returns a tensor with q's shape, dtype and layout.
+    Returns a tensor with q's shape, dtype and layout (and the LSE when asked for).
     """
     _reject_common(return_lse, kwargs)
     if sk1_backend is False or sk1_bf16 is False and q.dtype == torch.bfloat16:
@@ -62,7 +63,8 @@ def sageattn(
     if q.dtype == torch.float16 and sk1_int8 is not None:
         int8 = bool(sk1_int8)
     return _be.sage_call(q, k, v, tensor_layout=tensor_layout, is_causal=bool(is_causal),
-                         sm_scale=sm_scale, smooth_k=bool(kwargs.get("smooth_k", True)), int8=int8)
+                         sm_scale=sm_scale, smooth_k=bool(kwargs.get("smooth_k", True)), int8=int8,
+                         return_lse=bool(return_lse))
 
 
 def sageattn_qk_int8_pv_fp8(
@@ -90,7 +92,7 @@ def sageattn_qk_int8_pv_fp8(
     kwargs = dict(kwargs, smooth_v=smooth_v)
     _reject_common(return_lse, kwargs)
     return _be.sage_call(q, k, v, tensor_layout=tensor_layout, is_causal=bool(is_causal),
-                         sm_scale=sm_scale, smooth_k=bool(smooth_k), int8=None)
+                         sm_scale=sm_scale, smooth_k=bool(smooth_k), int8=None, return_lse=bool(return_lse))
 
 
 # upstream aliases kept so that existing call sites import unchanged

@@ -34,7 +34,7 @@ def test_attn_mask_lse_smooth_v_are_refused():
     q = _t(1, 1, 4, 128)
     with pytest.raises(NotImplementedError):
         sageattention.sageattn(q, q, q, attn_mask=torch.ones(4, 4))
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match="no CPU path"):      # return_lse is served, CPU tensors are not
         sageattention.sageattn(q, q, q, return_lse=True)
     with pytest.raises(NotImplementedError):
         sageattention.sageattn(q, q, q, smooth_v=True)
@@ -80,8 +80,11 @@ def test_accepted_views():
     (lambda q, k, v: (q, k, v.float()), "dtype"),
     (lambda q, k, v: (q.float(), k.float(), v.float()), "dtype"),
     (lambda q, k, v: (q[..., :64], k[..., :64], v[..., :64]), "stride_align"),
-    (lambda q, k, v: (q, k[:, :, :8], v[:, :, :8]), "seq_len"),
-    (lambda q, k, v: (q, k[:, :1], v[:, :1]), "heads"),
+    (lambda q, k, v: (q, k[:, :, :8], v), "seq_len"),                     # K and V lengths differ
+    (lambda q, k, v: (q, k[:, :, :8], v[:, :, :8]), None),                # a shorter K/V is served
+    (lambda q, k, v: (q, k[:, :1], v[:, :1]), None),                      # 2 query heads per K/V head
+    (lambda q, k, v: (q[:, :1], k, v), "heads"),                          # fewer query heads than K/V heads
+    (lambda q, k, v: (q, k[:, :1], v), "heads"),
     (lambda q, k, v: (q, k[:1], v[:1]), "batch"),
 ])
 def test_envelope_reasons(mutate, reason):
@@ -99,7 +102,7 @@ def test_envelope_reasons(mutate, reason):
 def test_envelope_layout_and_flags():
     q = _t(1, 1, 4, 128)
     assert be.envelope_reason(q, q, q, "HDN", require_cuda=False) == "layout"
-    assert be.envelope_reason(q, q, q, "HND", return_lse=True, require_cuda=False) == "return_lse"
+    assert be.envelope_reason(q, q, q, "HND", return_lse=True, require_cuda=False) is None
     assert be.envelope_reason(q, q, q, "HND", smooth_v=True, require_cuda=False) == "smooth_v"
     assert be.envelope_reason(q, q, q, "HND", attn_mask=q, require_cuda=False) == "attn_mask"
     assert be.envelope_reason(q, q, q, "HND", require_cuda=True) == "device"
