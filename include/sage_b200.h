@@ -144,43 +144,51 @@ int sage_attention(const void* q, const void* k, const void* v, void* out,
 /* ---- The same three entry points for the upstream call shapes the reference's hand-written path
  * refuses and hands to its other backends: grouped-query attention (Hq query heads sharing Hkv
  * key/value heads, Hq a multiple of Hkv), a key length different from the query length
- * (non-causal only), and the log-sum-exp output.  They replace, for those shapes, the fallback
+ * (non-causal only), the log-sum-exp output, and a head_dim below 128 (upstream zero-pads such
+ * heads to 64 or 128 columns on the host, sageattention/core.py:1524-1533; here the prologue reads
+ * `head_dim` columns per row and zero-fills the 128-wide codes itself, and the attention kernel
+ * writes `head_dim` output columns).  They replace, for those shapes, the fallback
  * `sageattn_qk_int8_pv_gfx12_native` (sageattention/core.py:470-1034) and follow the upstream
  * contract of `sageattn_qk_int8_pv_fp8_cuda` (sageattention/core.py:1747-1938: num_qo_heads a
  * multiple of num_kv_heads, return_lse with the smooth_k correction of :1893-1897,1935-1936).
  *
- *   q, out     logical (B,Hq,Nq,128); k, v logical (B,Hkv,Nk,128)
+ *   q, out     logical (B,Hq,Nq,head_dim); k, v logical (B,Hkv,Nk,head_dim);
+ *              head_dim a multiple of 8 in 8..128
  *   lse        optional (B*Hq, Nq) fp32: ln sum_k exp(sm_scale * q.k) of the UNquantised softmax
  *              the kernel evaluates (its row maximum and row sum), plus sm_scale * q.mean(K) when
  *              smooth_k is on, so that it refers to the caller's K, not the mean-subtracted one
  *   qm         (prologue output / attention input, optional) (B*Hq, Nq) fp32 q.mean(K); needed
  *              only when an LSE is wanted and smooth_k is on
+ *   vmean      (prologue output / attention input, optional) (B*Hkv, 128) fp32 mean of V over its
+ *              keys: upstream's `smooth_v` (sageattention/core.py:1917-1923, quant.py:297-301).  When
+ *              given, V minus this mean is what gets quantised and the attention kernel adds the
+ *              mean back to every output row (the softmax weights of a row sum to one)
  * Every size of K/V tensors (k8, sk, v8t, sv, svp, s_fold, mean, ctrl) is as for sage_prologue with
  * H = Hkv and N = Nk; q8 and sq are (B*Hq, Nq, 128) and (B*Hq, Nq). */
 int sage_prologue_ex(const void* q, const void* k, const void* v,
                      void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
-                     float* s_fold, float* mean, float* qm, void* ctrl,
+                     float* s_fold, float* mean, float* qm, float* vmean, void* ctrl,
                      int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad,
-                     const int64_t q_strides[3], const int64_t k_strides[3],
+                     int64_t head_dim, const int64_t q_strides[3], const int64_t k_strides[3],
                      const int64_t v_strides[3],
                      int dtype, int qk_mode, int smooth_k, void* stream);
 int sage_attn_fwd_ex(const void* q8, const float* sq, const void* k8, const float* sk,
                      const void* v8t, const float* svp, const float* s_fold, void* out,
-                     float* lse, const float* qm,
+                     float* lse, const float* qm, const float* vmean,
                      int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad,
-                     const int64_t o_strides[3], int causal, float sm_scale, int out_dtype,
+                     int64_t head_dim, const int64_t o_strides[3], int causal, float sm_scale, int out_dtype,
                      int qk_mode, int32_t* status, void* stream);
 size_t sage_workspace_bytes_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk);
 int sage_attention_ex(const void* q, const void* k, const void* v, void* out, float* lse,
                       void* workspace, size_t workspace_bytes,
-                      int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk,
+                      int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t head_dim,
                       const int64_t q_strides[3], const int64_t k_strides[3],
                       const int64_t v_strides[3], const int64_t o_strides[3],
-                      int dtype, int qk_mode, int causal, int smooth_k, float sm_scale,
+                      int dtype, int qk_mode, int causal, int smooth_k, int smooth_v, float sm_scale,
                       void* stream);
-/* As sage_workspace_layout, with a twelfth entry: qm. */
+/* As sage_workspace_layout, with two more entries: qm, vmean. */
 int sage_workspace_layout_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk,
-                             size_t offsets[12]);
+                             size_t offsets[13]);
 
 /* Offsets (bytes from `workspace`) of the intermediates sage_attention uses, for callers and
  * tests that want to look at them: order q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status.

@@ -108,14 +108,17 @@ def quant_k(k: torch.Tensor, mean: Optional[torch.Tensor], n_pad: int, int8: boo
     return k8, sk_out
 
 
-def quant_v(v: torch.Tensor, n_pad: int) -> Tuple[torch.Tensor, torch.Tensor]:
-    """V -> (V8 (B,H,n_pad,D) e4m3 in token-major order, SV (B,H,n_pad) f32).
+def quant_v(v: torch.Tensor, n_pad: int, mean: Optional[torch.Tensor] = None) -> Tuple[torch.Tensor, torch.Tensor]:
+    """V -> (V8 (B,H,n_pad,D) e4m3 in token-major order, SV (B,H,n_pad) f32).  With `mean`
+    (B,H,D), upstream's smooth_v (sageattention/quant.py:297-301), f32(V) - mean is quantised.
 
     sv = max(max_d|v| / 448, 1e-12); code = e4m3(min(v / sv, 448)); pad rows: code 0, SV = 0.0
     (h34_prologue.hip:168-211).  The reference stores the codes transposed, (B*H, D, n_pad);
     `v8.transpose(2, 3)` gives that view."""
     b, h, n, d = v.shape
     x = v.float()
+    if mean is not None:
+        x = x - mean[:, :, None, :]
     amax = x.abs().amax(dim=3)
     sv = torch.maximum(amax / _f32(F8_MAX, v.device), _f32(FLOOR, v.device))
     codes = e4m3_rne(torch.minimum(x / sv[..., None], _f32(F8_MAX, v.device)))
@@ -163,7 +166,8 @@ def row_score_scale(sq: torch.Tensor, sm_scale: float) -> torch.Tensor:
 def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tensor,
            v8: torch.Tensor, svp: torch.Tensor, s_fold: torch.Tensor, n: int, causal: bool,
            sm_scale: float, out_dtype: torch.dtype, tile: int = REF_BN,
-           row_chunk: int = 2048, row0: int = 0, return_lse: bool = False):
+           row_chunk: int = 2048, row0: int = 0, return_lse: bool = False,
+           vmean: Optional[torch.Tensor] = None):
     """The attention loop of sk1_t6i.hip:151-299 on already-quantised operands.
 
     q8 (B,H,R,D), sq (B,H,R) hold the query rows row0 .. row0+R-1 (all N rows by default); k8, v8
@@ -179,7 +183,9 @@ def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tenso
     heads than q8 (grouped-query attention; every group of Hq/Hkv query heads shares a K/V head),
     the number of keys may differ from the number of queries when not causal, and with
     `return_lse` the function also returns ln2 * (m + log2 l), the log-sum-exp of the
-    mean-subtracted logits (callers add sm_scale * q.mean(K) for the caller's K)."""
+    mean-subtracted logits (callers add sm_scale * q.mean(K) for the caller's K).  `vmean`
+    (B,Hkv,D), the mean that smooth_v subtracted from V, is added to every output row in fp32
+    before the cast (sk1_t6i.hip:297 `acc*inv + vm`)."""
     prev_tf32 = torch.backends.cuda.matmul.allow_tf32
     torch.backends.cuda.matmul.allow_tf32 = False
     try:
@@ -191,6 +197,7 @@ def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tenso
             k8, v8 = k8.repeat_interleave(g, dim=1), v8.repeat_interleave(g, dim=1)
             sk, svp = sk.repeat_interleave(g, dim=1), svp.repeat_interleave(g, dim=1)
             s_fold = s_fold.repeat_interleave(g, dim=1)
+            vmean = vmean.repeat_interleave(g, dim=1) if vmean is not None else None
         dev = q8.device
         kf = k8.float()
         vf = v8.float()
@@ -228,7 +235,10 @@ def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tenso
                 p8 = e4m3_rne(p * stage[:, :, None, c0:c1]).float()
                 acc = acc * alpha[..., None] + torch.matmul(p8, vf[:, :, c0:c1])
             inv = torch.where(l > 0, s_fold[..., None] / (l * _f32(F8_MAX, dev)), torch.zeros_like(l))
-            out[:, :, r0:r1] = (acc * inv[..., None]).to(out_dtype)
+            res = acc * inv[..., None]
+            if vmean is not None:
+                res = res + vmean[:, :, None, :]
+            out[:, :, r0:r1] = res.to(out_dtype)
             lse[:, :, r0:r1] = math.log(2.0) * (m + torch.log2(l))
         return (out, lse) if return_lse else out
     finally:
@@ -236,7 +246,7 @@ def attend(q8: torch.Tensor, sq: torch.Tensor, k8: torch.Tensor, sk: torch.Tenso
 
 
 def prologue(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool = True,
-             int8: Optional[bool] = None, pad_multiple: int = REF_BN) -> dict:
+             int8: Optional[bool] = None, pad_multiple: int = REF_BN, smooth_v: bool = False) -> dict:
     """The whole quantisation prologue on logical (B,H,N,D) tensors.  `int8=None` picks the
     reference's default: int8 Q.K for fp16 inputs, e4m3 Q.K for bf16
     (sageattention/sk1_backend/__init__.py:1045-1060)."""
@@ -247,16 +257,17 @@ def prologue(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool =
     mean = kseq_mean(k) if smooth_k else None
     q8, sq = quant_q(q, int8)
     k8, sk = quant_k(k, mean, n_pad, int8)
-    v8, sv = quant_v(v, n_pad)
+    vmean = kseq_mean(v) if smooth_v else None      # same fp64 accumulation as the K mean
+    v8, sv = quant_v(v, n_pad, vmean)
     svp, s_fold = fold_v_scale(sv)
-    return dict(q8=q8, sq=sq, k8=k8, sk=sk, v8=v8, sv=sv, svp=svp, S=s_fold, mean=mean,
+    return dict(q8=q8, sq=sq, k8=k8, sk=sk, v8=v8, sv=sv, svp=svp, S=s_fold, mean=mean, vmean=vmean,
                 n=n, n_pad=n_pad, int8=int8)
 
 
 def sageattn_oracle(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_layout: str = "HND",
                     is_causal: bool = False, sm_scale: Optional[float] = None,
                     smooth_k: bool = True, int8: Optional[bool] = None,
-                    tile: int = REF_BN, return_lse: bool = False):
+                    tile: int = REF_BN, return_lse: bool = False, smooth_v: bool = False):
     """The reference call end to end (sageattention/sk1_backend/__init__.py:982-1284): output has
     q's shape, dtype and layout; sm_scale defaults to D**-0.5 (:1165)."""
     if tensor_layout == "NHD":
@@ -266,9 +277,9 @@ def sageattn_oracle(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, tensor_la
     d = q.shape[3]
     if sm_scale is None:
         sm_scale = d ** -0.5
-    pq = prologue(q, k, v, smooth_k=smooth_k, int8=int8, pad_multiple=tile)
+    pq = prologue(q, k, v, smooth_k=smooth_k, int8=int8, pad_multiple=tile, smooth_v=smooth_v)
     res = attend(pq["q8"], pq["sq"], pq["k8"], pq["sk"], pq["v8"], pq["svp"], pq["S"], pq["n"],
-                 is_causal, float(sm_scale), q.dtype, tile=tile, return_lse=return_lse)
+                 is_causal, float(sm_scale), q.dtype, tile=tile, return_lse=return_lse, vmean=pq["vmean"])
     out = res[0] if return_lse else res
     if tensor_layout == "NHD":
         out = out.transpose(1, 2)

@@ -17,7 +17,7 @@
 //   p  = exp2(c_q*u - c_q*m); l = l*alpha + sum(p); P8 = e4m3(p * svp[key]) written to shared
 //        memory in the 128-byte swizzled K-major layout
 //   O += P8 . V8            kind::f8f6f4 into TMEM cols 128..255
-// Epilogue: out = O * (S_fold / (l * 448)) -> fp16 / bf16.
+// Epilogue: out = O * (S_fold / (l * 448)) (+ mean of V with smooth_v) -> fp16 / bf16.
 // (numerics: kernels/hip/sk1_t6i.hip:151-299 and kernels/hip/sk1_t4a1sb.hip:176-189 of the
 // reference, with a 128-key instead of a 64-key tile for the running max; the two score factors
 // c_q and sk are applied one after the other instead of as one pre-multiplied factor, a
@@ -122,12 +122,10 @@ __device__ __forceinline__ void mbar_arrive_lane0(uint32_t bar, int lane) {
 // Four floats -> four e4m3 bytes in memory order (a lowest), round to nearest even, saturating.
 __device__ __forceinline__ uint32_t e4m3x4_pack(float a, float b, float c, float d) {
   uint32_t w;
-  asm("{\n\t.reg .b16 lo, hi;\n\t.reg .b32 l32, h32;\n\t"
+  asm("{\n\t.reg .b16 lo, hi;\n\t"
       "cvt.rn.satfinite.e4m3x2.f32 lo, %2, %1;\n\t"
       "cvt.rn.satfinite.e4m3x2.f32 hi, %4, %3;\n\t"
-      "cvt.u32.u16 l32, lo;\n\t"
-      "cvt.u32.u16 h32, hi;\n\t"
-      "prmt.b32 %0, l32, h32, 0x5410;\n\t}"
+      "mov.b32 %0, {lo, hi};\n\t}"
       : "=r"(w) : "f"(a), "f"(b), "f"(c), "f"(d));
   return w;
 }
@@ -266,8 +264,10 @@ struct AttnKArgs {
   void* out;
   long long N, N_pad, H;          // keys: length, padded length, K/V heads per batch element
   long long Nq, Hq, group;        // queries: length, heads per batch element, Hq / H
+  int D;                          // columns of an output row that exist (head_dim <= 128)
   float* lse;                     // optional (B*Hq, Nq)
   const float* qm;                // optional: dot(q row, K mean), added to the LSE (times sm_scale)
+  const float* vmean;             // optional (B*H, 128): added to every output row (smooth_v)
   long long o_sb, o_sh, o_sr;
   float sm_scale;
   int32_t* status;
@@ -593,12 +593,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (q_row < a.Nq) {
 #pragma unroll
             for (int g = 0; g < 4; ++g) {
+              float f[8];
+#pragma unroll
+              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[8 * g + e]) * inv;
+              if (a.vmean != nullptr) {             // smooth_v: the rows of P sum to one, so add the mean back
+                const float4* vm = reinterpret_cast<const float4*>(a.vmean + (size_t)bh_kv * HD + 64 * half + 32 * i + 8 * g);
+                const float4 v0 = __ldg(vm), v1 = __ldg(vm + 1);
+                f[0] += v0.x; f[1] += v0.y; f[2] += v0.z; f[3] += v0.w;
+                f[4] += v1.x; f[5] += v1.y; f[6] += v1.z; f[7] += v1.w;
+              }
               uint4 w;
-              w.x = pack2<OutT>(__uint_as_float(o[8 * g + 0]) * inv, __uint_as_float(o[8 * g + 1]) * inv);
-              w.y = pack2<OutT>(__uint_as_float(o[8 * g + 2]) * inv, __uint_as_float(o[8 * g + 3]) * inv);
-              w.z = pack2<OutT>(__uint_as_float(o[8 * g + 4]) * inv, __uint_as_float(o[8 * g + 5]) * inv);
-              w.w = pack2<OutT>(__uint_as_float(o[8 * g + 6]) * inv, __uint_as_float(o[8 * g + 7]) * inv);
-              *reinterpret_cast<uint4*>(orow + 32 * i + 8 * g) = w;
+              w.x = pack2<OutT>(f[0], f[1]);
+              w.y = pack2<OutT>(f[2], f[3]);
+              w.z = pack2<OutT>(f[4], f[5]);
+              w.w = pack2<OutT>(f[6], f[7]);
+              if (64 * half + 32 * i + 8 * g < a.D) *reinterpret_cast<uint4*>(orow + 32 * i + 8 * g) = w;
             }
           }
         }
@@ -692,7 +701,7 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   AttnKArgs ka;
   ka.sq = p.sq; ka.sk = p.sk; ka.svp = p.svp; ka.s_fold = p.s_fold; ka.out = p.out;
   ka.N = p.N; ka.N_pad = p.N_pad; ka.H = p.H;
-  ka.Nq = p.Nq; ka.Hq = p.Hq; ka.group = p.Hq / p.H; ka.lse = p.lse; ka.qm = p.qm;
+  ka.Nq = p.Nq; ka.Hq = p.Hq; ka.group = p.Hq / p.H; ka.lse = p.lse; ka.qm = p.qm; ka.D = (int)p.D; ka.vmean = p.vmean;
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
   ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;

@@ -69,15 +69,17 @@ int check_strides(const char* name, const int64_t s[3]) {
 }
 
 // Shape of one call: B batches; Hq query heads sharing Hkv key/value heads (Hq a multiple of Hkv);
-// Nq query rows; Nk keys.
+// Nq query rows; Nk keys; D elements per q/k/v/out row (the quantised codes are always 128 wide).
 struct Dims {
-  int64_t B, Hq, Hkv, Nq, Nk;
+  int64_t B, Hq, Hkv, Nq, Nk, D;
 };
 
 int check_dims(const Dims& d) {
   if (d.B < 1 || d.Hq < 1 || d.Hkv < 1 || d.Nq < 1 || d.Nk < 1)
     return fail(SAGE_E_ARG, "B, heads and lengths must be >= 1 (got B=%lld Hq=%lld Hkv=%lld Nq=%lld Nk=%lld)",
                 (long long)d.B, (long long)d.Hq, (long long)d.Hkv, (long long)d.Nq, (long long)d.Nk);
+  if (d.D < 8 || d.D > sage::HD || d.D % 8)
+    return fail(SAGE_E_UNSUPPORTED, "head_dim must be a multiple of 8 in 8..128 (got %lld)", (long long)d.D);
   if (d.Hq % d.Hkv) return fail(SAGE_E_ARG, "query heads (%lld) must be a multiple of key/value heads (%lld)",
                                 (long long)d.Hq, (long long)d.Hkv);
   if (d.B * d.Hq > 65535) return fail(SAGE_E_UNSUPPORTED, "B*H = %lld exceeds the grid limit 65535", (long long)(d.B * d.Hq));
@@ -86,7 +88,7 @@ int check_dims(const Dims& d) {
 }
 
 struct Layout {
-  size_t q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status, qm, total;
+  size_t q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status, qm, vmean, total;
 };
 
 Layout carve(const Dims& d) {
@@ -107,13 +109,14 @@ Layout carve(const Dims& d) {
   L.ctrl = take(sage::prologue_ctrl_bytes(d.B, d.Hkv, d.Nk));
   L.status = take(256);
   L.qm = take(bhq * nq * 4);
+  L.vmean = take(bhk * sage::HD * 4);
   L.total = off;
   return L;
 }
 
 int prologue_impl(const void* q, const void* k, const void* v,
                   void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
-                  float* s_fold, float* mean, float* qm, void* ctrl, const Dims& d, int64_t Nk_pad,
+                  float* s_fold, float* mean, float* qm, float* vmean, void* ctrl, const Dims& d, int64_t Nk_pad,
                   const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                   int dtype, int qk_mode, int smooth_k, void* stream, const char* who) {
   g_err[0] = 0;
@@ -133,8 +136,8 @@ int prologue_impl(const void* q, const void* k, const void* v,
     return fail(SAGE_E_ARG, "%s: pointers must be 16-byte aligned", who);
   sage::PrologueParams p;
   p.q = q; p.k = k; p.v = v; p.q8 = q8; p.k8 = k8; p.v8t = v8t;
-  p.sq = sq; p.sk = sk; p.sv = sv; p.svp = svp; p.s_fold = s_fold; p.mean = mean; p.ctrl = ctrl; p.qm = qm;
-  p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq;
+  p.sq = sq; p.sk = sk; p.sv = sv; p.svp = svp; p.s_fold = s_fold; p.mean = mean; p.ctrl = ctrl; p.qm = qm; p.vmean = vmean;
+  p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq; p.D = d.D;
   for (int i = 0; i < 3; ++i) { p.q_strides[i] = q_strides[i]; p.k_strides[i] = k_strides[i]; p.v_strides[i] = v_strides[i]; }
   p.dtype = dtype; p.qk_mode = qk_mode; p.smooth_k = smooth_k;
   cudaError_t e = sage::launch_prologue(p, reinterpret_cast<cudaStream_t>(stream));
@@ -144,7 +147,7 @@ int prologue_impl(const void* q, const void* k, const void* v,
 
 int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
               const void* v8t, const float* svp, const float* s_fold, void* out, float* lse, const float* qm,
-              const Dims& d, int64_t Nk_pad, const int64_t o_strides[3],
+              const float* vmean, const Dims& d, int64_t Nk_pad, const int64_t o_strides[3],
               int causal, float sm_scale, int out_dtype, int qk_mode, int32_t* status, void* stream,
               const char* who) {
   g_err[0] = 0;
@@ -162,8 +165,8 @@ int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
   if (!(sm_scale == sm_scale)) return fail(SAGE_E_ARG, "%s: sm_scale is NaN", who);
   sage::AttnParams p;
   p.q8 = q8; p.k8 = k8; p.v8t = v8t; p.sq = sq; p.sk = sk; p.svp = svp; p.s_fold = s_fold; p.out = out;
-  p.lse = lse; p.qm = qm;
-  p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq;
+  p.lse = lse; p.qm = qm; p.vmean = vmean;
+  p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq; p.D = d.D;
   for (int i = 0; i < 3; ++i) p.o_strides[i] = o_strides[i];
   p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.out_dtype = out_dtype; p.qk_mode = qk_mode;
   p.status = status;
@@ -177,7 +180,7 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
                    void* workspace, size_t workspace_bytes, const Dims& d,
                    const int64_t q_strides[3], const int64_t k_strides[3],
                    const int64_t v_strides[3], const int64_t o_strides[3],
-                   int dtype, int qk_mode, int causal, int smooth_k, float sm_scale, void* stream,
+                   int dtype, int qk_mode, int causal, int smooth_k, int smooth_v, float sm_scale, void* stream,
                    const char* who) {
   g_err[0] = 0;
   int rc = check_dims(d);
@@ -194,15 +197,16 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
   cudaError_t e = cudaMemsetAsync(status, 0, 4, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s", who, cudaGetErrorString(e));
   float* qm = (lse && smooth_k) ? reinterpret_cast<float*>(w + L.qm) : nullptr;
+  float* vmean = smooth_v ? reinterpret_cast<float*>(w + L.vmean) : nullptr;
   rc = prologue_impl(q, k, v, w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
                      reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.sv),
                      reinterpret_cast<float*>(w + L.svp), reinterpret_cast<float*>(w + L.s_fold),
-                     reinterpret_cast<float*>(w + L.mean), qm, w + L.ctrl, d, Nk_pad,
+                     reinterpret_cast<float*>(w + L.mean), qm, vmean, w + L.ctrl, d, Nk_pad,
                      q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, who);
   if (rc) return rc;
   return attn_impl(w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
                    reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.svp),
-                   reinterpret_cast<float*>(w + L.s_fold), out, lse, qm, d, Nk_pad, o_strides,
+                   reinterpret_cast<float*>(w + L.s_fold), out, lse, qm, vmean, d, Nk_pad, o_strides,
                    causal, sm_scale, dtype, qk_mode, status, stream, who);
 }
 
@@ -227,19 +231,19 @@ int sage_prologue(const void* q, const void* k, const void* v,
                   int64_t B, int64_t H, int64_t N, int64_t N_pad,
                   const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                   int dtype, int qk_mode, int smooth_k, void* stream) {
-  const Dims d = {B, H, H, N, N};
-  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, nullptr, ctrl, d, N_pad,
+  const Dims d = {B, H, H, N, N, sage::HD};
+  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, nullptr, nullptr, ctrl, d, N_pad,
                        q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, "sage_prologue");
 }
 
 int sage_prologue_ex(const void* q, const void* k, const void* v,
                      void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
-                     float* s_fold, float* mean, float* qm, void* ctrl,
-                     int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad,
+                     float* s_fold, float* mean, float* qm, float* vmean, void* ctrl,
+                     int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad, int64_t head_dim,
                      const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                      int dtype, int qk_mode, int smooth_k, void* stream) {
-  const Dims d = {B, Hq, Hkv, Nq, Nk};
-  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, qm, ctrl, d, Nk_pad,
+  const Dims d = {B, Hq, Hkv, Nq, Nk, head_dim};
+  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, qm, vmean, ctrl, d, Nk_pad,
                        q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, "sage_prologue_ex");
 }
 
@@ -253,7 +257,7 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
                               const int64_t v_strides[3],
                               int dtype, int qk_mode, int smooth_k, void* stream) {
   g_err[0] = 0;
-  const Dims d = {B, H, H, N, N};
+  const Dims d = {B, H, H, N, N, sage::HD};
   int rc = check_dims(d);
   if (rc) return rc;
   const size_t need = sage::prologue_ctrl_bytes(B, H, N);
@@ -264,7 +268,7 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
   void* ctrl = nullptr;
   rc = static_ctrl_address(&ctrl);
   if (rc) return rc;
-  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, nullptr, ctrl, d, N_pad,
+  return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, nullptr, nullptr, ctrl, d, N_pad,
                        q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream,
                        "sage_prologue_static_ctrl");
 }
@@ -274,19 +278,19 @@ int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* 
                   int64_t B, int64_t H, int64_t N, int64_t N_pad, const int64_t o_strides[3],
                   int causal, float sm_scale, int out_dtype, int qk_mode,
                   int32_t* status, void* stream) {
-  const Dims d = {B, H, H, N, N};
-  return attn_impl(q8, sq, k8, sk, v8t, svp, s_fold, out, nullptr, nullptr, d, N_pad, o_strides,
+  const Dims d = {B, H, H, N, N, sage::HD};
+  return attn_impl(q8, sq, k8, sk, v8t, svp, s_fold, out, nullptr, nullptr, nullptr, d, N_pad, o_strides,
                    causal, sm_scale, out_dtype, qk_mode, status, stream, "sage_attn_fwd");
 }
 
 int sage_attn_fwd_ex(const void* q8, const float* sq, const void* k8, const float* sk,
                      const void* v8t, const float* svp, const float* s_fold, void* out,
-                     float* lse, const float* qm,
-                     int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad,
+                     float* lse, const float* qm, const float* vmean,
+                     int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t Nk_pad, int64_t head_dim,
                      const int64_t o_strides[3], int causal, float sm_scale, int out_dtype, int qk_mode,
                      int32_t* status, void* stream) {
-  const Dims d = {B, Hq, Hkv, Nq, Nk};
-  return attn_impl(q8, sq, k8, sk, v8t, svp, s_fold, out, lse, qm, d, Nk_pad, o_strides,
+  const Dims d = {B, Hq, Hkv, Nq, Nk, head_dim};
+  return attn_impl(q8, sq, k8, sk, v8t, svp, s_fold, out, lse, qm, vmean, d, Nk_pad, o_strides,
                    causal, sm_scale, out_dtype, qk_mode, status, stream, "sage_attn_fwd_ex");
 }
 
@@ -294,34 +298,34 @@ void sage_debug_score_dump(void* ptr, int key_tile) { sage::set_score_dump(ptr, 
 
 size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N) {
   if (B < 1 || H < 1 || N < 1) return 0;
-  const Dims d = {B, H, H, N, N};
+  const Dims d = {B, H, H, N, N, sage::HD};
   return carve(d).total;
 }
 
 size_t sage_workspace_bytes_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk) {
-  const Dims d = {B, Hq, Hkv, Nq, Nk};
+  const Dims d = {B, Hq, Hkv, Nq, Nk, sage::HD};
   if (B < 1 || Hq < 1 || Hkv < 1 || Nq < 1 || Nk < 1 || Hq % Hkv) return 0;
   return carve(d).total;
 }
 
 static int layout_out(const Dims& d, size_t* offsets, int n) {
   const Layout L = carve(d);
-  const size_t o[12] = {L.q8, L.sq, L.k8, L.sk, L.v8t, L.sv, L.svp, L.s_fold, L.mean, L.ctrl, L.status, L.qm};
+  const size_t o[13] = {L.q8, L.sq, L.k8, L.sk, L.v8t, L.sv, L.svp, L.s_fold, L.mean, L.ctrl, L.status, L.qm, L.vmean};
   memcpy(offsets, o, sizeof(size_t) * (size_t)n);
   return n;
 }
 
 int sage_workspace_layout(int64_t B, int64_t H, int64_t N, size_t offsets[11]) {
   if (B < 1 || H < 1 || N < 1 || !offsets) return fail(SAGE_E_ARG, "sage_workspace_layout: bad argument");
-  const Dims d = {B, H, H, N, N};
+  const Dims d = {B, H, H, N, N, sage::HD};
   return layout_out(d, offsets, 11);
 }
 
-int sage_workspace_layout_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, size_t offsets[12]) {
+int sage_workspace_layout_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, size_t offsets[13]) {
   if (B < 1 || Hq < 1 || Hkv < 1 || Nq < 1 || Nk < 1 || Hq % Hkv || !offsets)
     return fail(SAGE_E_ARG, "sage_workspace_layout_ex: bad argument");
-  const Dims d = {B, Hq, Hkv, Nq, Nk};
-  return layout_out(d, offsets, 12);
+  const Dims d = {B, Hq, Hkv, Nq, Nk, sage::HD};
+  return layout_out(d, offsets, 13);
 }
 
 int sage_attention(const void* q, const void* k, const void* v, void* out,
@@ -330,20 +334,20 @@ int sage_attention(const void* q, const void* k, const void* v, void* out,
                    const int64_t q_strides[3], const int64_t k_strides[3],
                    const int64_t v_strides[3], const int64_t o_strides[3],
                    int dtype, int qk_mode, int causal, int smooth_k, float sm_scale, void* stream) {
-  const Dims d = {B, H, H, N, N};
+  const Dims d = {B, H, H, N, N, sage::HD};
   return attention_impl(q, k, v, out, nullptr, workspace, workspace_bytes, d, q_strides, k_strides, v_strides,
-                        o_strides, dtype, qk_mode, causal, smooth_k, sm_scale, stream, "sage_attention");
+                        o_strides, dtype, qk_mode, causal, smooth_k, 0, sm_scale, stream, "sage_attention");
 }
 
 int sage_attention_ex(const void* q, const void* k, const void* v, void* out, float* lse,
                       void* workspace, size_t workspace_bytes,
-                      int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk,
+                      int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk, int64_t head_dim,
                       const int64_t q_strides[3], const int64_t k_strides[3],
                       const int64_t v_strides[3], const int64_t o_strides[3],
-                      int dtype, int qk_mode, int causal, int smooth_k, float sm_scale, void* stream) {
-  const Dims d = {B, Hq, Hkv, Nq, Nk};
+                      int dtype, int qk_mode, int causal, int smooth_k, int smooth_v, float sm_scale, void* stream) {
+  const Dims d = {B, Hq, Hkv, Nq, Nk, head_dim};
   return attention_impl(q, k, v, out, lse, workspace, workspace_bytes, d, q_strides, k_strides, v_strides,
-                        o_strides, dtype, qk_mode, causal, smooth_k, sm_scale, stream, "sage_attention_ex");
+                        o_strides, dtype, qk_mode, causal, smooth_k, smooth_v, sm_scale, stream, "sage_attention_ex");
 }
 
 }  // extern "C"

@@ -12,8 +12,10 @@ struct PrologueParams {
   float *sq, *sk, *sv, *svp, *s_fold, *mean;
   void* ctrl;
   float* qm;                                           // optional (B*Hq, Nq): q . K-mean, for the LSE
+  float* vmean;                                        // optional (B*H, 128): smooth_v subtracts the sequence mean of V
   int64_t B, H, N, N_pad;                              // K/V side: heads, keys, padded keys
   int64_t Hq, Nq;                                      // query side (Hq a multiple of H)
+  int64_t D;                                           // head_dim of q/k/v rows (multiple of 8, <= 128); codes are 128 wide, zero-filled
   int64_t q_strides[3], k_strides[3], v_strides[3];   // (batch, head, row) in elements
   int dtype;      // 0 fp16, 1 bf16
   int qk_mode;    // 0 int8, 1 e4m3
@@ -26,8 +28,10 @@ struct AttnParams {
   void* out;
   float* lse;                                          // optional (B*Hq, Nq) natural-log sum of exponentials
   const float* qm;                                     // with lse and smooth_k: q . K-mean per query row
+  const float* vmean;                                  // with smooth_v: (B*H, 128) mean of V, added back to every output row
   int64_t B, H, N, N_pad;                              // K/V side: heads, keys, padded keys
   int64_t Hq, Nq;                                      // query side
+  int64_t D;                                           // columns of an output row that exist (head_dim)
   int64_t o_strides[3];                                // (batch, head, row) in elements
   int causal;
   float sm_scale;

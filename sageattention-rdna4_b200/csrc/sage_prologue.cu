@@ -31,7 +31,7 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restrict__ partial,
              unsigned* __restrict__ arrivals, long long N, long long H,
-             long long sb, long long sh, long long sr, int nsplit, long long chunk) {
+             long long sb, long long sh, long long sr, int nsplit, long long chunk, int D) {
   __shared__ double red[16][HD];
   __shared__ int s_last;
   const int tid = threadIdx.x, c = tid & 15, r = tid >> 4;
@@ -44,8 +44,9 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
   double acc[8];
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.0;
+  const long long n_end = (8 * c < D) ? n1 : n0;   // columns past head_dim: nothing to read, mean 0
 #pragma unroll 8
-  for (long long n = n0 + r; n < n1; n += 16) {
+  for (long long n = n0 + r; n < n_end; n += 16) {
     const uint4 u = __ldg(reinterpret_cast<const uint4*>(base + n * sr));
     float x[8];
     unpack8<T>(u, x);
@@ -93,6 +94,7 @@ struct QuantArgs {
   uint8_t *q8, *k8, *v8t;
   float *sq, *sk, *sv, *svp, *s_fold;
   const float* mean;
+  const float* vmean;             // optional: sequence mean of V, subtracted before quantising (smooth_v)
   unsigned *arrivals, *svmax_bits;
   long long N, N_pad, H;          // keys: length, padded length, K/V heads per batch element
   long long Nq, Hq, group;        // queries: length, heads per batch element, Hq / H (1 without GQA)
@@ -100,6 +102,7 @@ struct QuantArgs {
   float* qm;                      // optional (B*Hq, Nq): dot(q row, K mean of its K/V head), for the LSE
   long long q_sb, q_sh, q_sr, k_sb, k_sh, k_sr, v_sb, v_sh, v_sr;
   int sub_mean;
+  int D;                          // head_dim of the q/k/v rows; code columns D..127 are zero
 };
 
 __device__ __forceinline__ float half_warp_max(float x) {
@@ -112,11 +115,11 @@ __device__ __forceinline__ float half_warp_max(float x) {
 
 template <typename T>
 __device__ __forceinline__ void load_rows(const T* base, long long sr, long long n_base, int r0,
-                                          long long N, uint4* raw) {
+                                          long long N, bool col_live, uint4* raw) {
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     const long long n = n_base + r0 + 16 * i;
-    raw[i] = (n < N) ? __ldg(reinterpret_cast<const uint4*>(base + n * sr)) : make_uint4(0, 0, 0, 0);
+    raw[i] = (n < N && col_live) ? __ldg(reinterpret_cast<const uint4*>(base + n * sr)) : make_uint4(0, 0, 0, 0);
   }
 }
 
@@ -146,6 +149,7 @@ quant_qkv_kernel(const QuantArgs a) {
   const int which = blockIdx.z == 0 ? 1 : (blockIdx.z == 1 ? 0 : 2);   // 0 Q, 1 K, 2 V; K tiles are issued first
   const long long n_base = (long long)blockIdx.x * TILE;
   uint4 raw[8];
+  const bool col_live = 8 * c < a.D;
 
   if (which == 0) {
     // ---------------------------------- Q ----------------------------------
@@ -153,7 +157,7 @@ quant_qkv_kernel(const QuantArgs a) {
     if (bh >= a.BHq || n_base >= N) return;
     const long long b = bh / a.Hq, h = bh - b * a.Hq;
     const T* qb = reinterpret_cast<const T*>(a.q) + b * a.q_sb + h * a.q_sh + 8 * c;
-    load_rows<T>(qb, a.q_sr, n_base, r0, N, raw);
+    load_rows<T>(qb, a.q_sr, n_base, r0, N, col_live, raw);
     float mu[8];
     if (a.qm != nullptr) {                            // the K mean of this query head's K/V head
       const long long bh_kv = b * a.H + h / a.group;
@@ -208,7 +212,7 @@ quant_qkv_kernel(const QuantArgs a) {
   if (which == 1) {
     // ---------------------------------- K ----------------------------------
     const T* kb = reinterpret_cast<const T*>(a.k) + b * a.k_sb + h * a.k_sh + 8 * c;
-    load_rows<T>(kb, a.k_sr, n_base, r0, N, raw);
+    load_rows<T>(kb, a.k_sr, n_base, r0, N, col_live, raw);
     float mu[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) mu[e] = a.sub_mean ? a.mean[(size_t)bh * HD + 8 * c + e] : 0.f;
@@ -221,7 +225,7 @@ quant_qkv_kernel(const QuantArgs a) {
       float amax = 0.f;
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
-        x[e] = live ? __fsub_rn(x[e], mu[e]) : 0.f;
+        x[e] = (live && col_live) ? __fsub_rn(x[e], mu[e]) : 0.f;
         amax = fmaxf(amax, fabsf(x[e]));
       }
       amax = half_warp_max(amax);
@@ -250,7 +254,10 @@ quant_qkv_kernel(const QuantArgs a) {
   float svmax = 0.f;
   {
     const T* vb = reinterpret_cast<const T*>(a.v) + b * a.v_sb + h * a.v_sh + 8 * c;
-    load_rows<T>(vb, a.v_sr, n_base, r0, N, raw);
+    load_rows<T>(vb, a.v_sr, n_base, r0, N, col_live, raw);
+    float vmu[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) vmu[e] = a.vmean ? a.vmean[(size_t)bh * HD + 8 * c + e] : 0.f;
 #pragma unroll
     for (int i = 0; i < 8; ++i) {
       const int t = r0 + 16 * i;                    // token within the tile; its 16-group is i
@@ -260,7 +267,10 @@ quant_qkv_kernel(const QuantArgs a) {
       unpack8<T>(raw[i], x);
       float amax = 0.f;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(x[e]));
+      for (int e = 0; e < 8; ++e) {
+        if (a.vmean) x[e] = (live && col_live) ? __fsub_rn(x[e], vmu[e]) : 0.f;
+        amax = fmaxf(amax, fabsf(x[e]));
+      }
       amax = half_warp_max(amax);
       const float sv = fmaxf(__fdiv_rn(amax, F8_MAX), SCALE_FLOOR);
       const float rc = __frcp_rn(sv);
@@ -351,7 +361,18 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     dim3 grid(nsplit, (unsigned)bh);
     kmean_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.k), p.mean, partial, words,
                                           p.N, p.H, p.k_strides[0], p.k_strides[1], p.k_strides[2],
-                                          nsplit, chunk);
+                                          nsplit, chunk, (int)p.D);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return e;
+  }
+  if (p.vmean) {
+    const int nsplit = kmean_splits(bh, p.N);
+    long long chunk = (p.N + nsplit - 1) / nsplit;
+    chunk = (chunk + 15) / 16 * 16;
+    dim3 grid(nsplit, (unsigned)bh);
+    kmean_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.v), p.vmean, partial, words + 3 * bh,
+                                          p.N, p.H, p.v_strides[0], p.v_strides[1], p.v_strides[2],
+                                          nsplit, chunk, (int)p.D);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -359,7 +380,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   a.q = p.q; a.k = p.k; a.v = p.v;
   a.q8 = reinterpret_cast<uint8_t*>(p.q8); a.k8 = reinterpret_cast<uint8_t*>(p.k8);
   a.v8t = reinterpret_cast<uint8_t*>(p.v8t);
-  a.sq = p.sq; a.sk = p.sk; a.sv = p.sv; a.svp = p.svp; a.s_fold = p.s_fold; a.mean = p.mean;
+  a.sq = p.sq; a.sk = p.sk; a.sv = p.sv; a.svp = p.svp; a.s_fold = p.s_fold; a.mean = p.mean; a.vmean = p.vmean;
   a.arrivals = words + bh; a.svmax_bits = words + 2 * bh;
   a.N = p.N; a.N_pad = p.N_pad; a.H = p.H;
   a.Nq = p.Nq; a.Hq = p.Hq; a.group = p.Hq / p.H; a.BHq = p.B * p.Hq; a.BHkv = bh; a.qm = p.qm;
@@ -367,6 +388,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   a.k_sb = p.k_strides[0]; a.k_sh = p.k_strides[1]; a.k_sr = p.k_strides[2];
   a.v_sb = p.v_strides[0]; a.v_sh = p.v_strides[1]; a.v_sr = p.v_strides[2];
   a.sub_mean = p.smooth_k ? 1 : 0;
+  a.D = (int)p.D;
   const int64_t tq = (p.Nq + TILE - 1) / TILE, tk = p.N_pad / TILE;
   dim3 grid((unsigned)(tq > tk ? tq : tk), (unsigned)(a.BHq > bh ? a.BHq : bh), 3);
   if (p.qk_mode == 0) quant_qkv_kernel<T, true><<<grid, 256, 0, st>>>(a);

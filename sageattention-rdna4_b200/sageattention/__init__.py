@@ -14,6 +14,7 @@ from .core import (  # noqa: F401
     sageattn_qk_int8_pv_fp8,
     sageattn_qk_int8_pv_fp8_cuda,
     sageattn_qk_int8_pv_fp8_cuda_sm90,
+    sageattn_varlen,
 )
 from .b200_backend import status  # noqa: F401
 from .sharding import partition_units, sageattn_sharded, gather_units  # noqa: F401
@@ -25,6 +26,7 @@ __all__ = [
     "sageattn_qk_int8_pv_fp8",
     "sageattn_qk_int8_pv_fp8_cuda",
     "sageattn_qk_int8_pv_fp8_cuda_sm90",
+    "sageattn_varlen",
     "partition_units",
     "sageattn_sharded",
     "gather_units",

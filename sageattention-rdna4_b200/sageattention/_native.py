@@ -38,17 +38,17 @@ SIGNATURES = {
     "sage_attn_fwd": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P,
                                      _I64, _I64, _I64, _I64, _S3,
                                      ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int, _P, _P]),
-    "sage_prologue_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
-                                        _I64, _I64, _I64, _I64, _I64, _I64, _S3, _S3, _S3,
+    "sage_prologue_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                        _I64, _I64, _I64, _I64, _I64, _I64, _I64, _S3, _S3, _S3,
                                         ctypes.c_int, ctypes.c_int, ctypes.c_int, _P]),
-    "sage_attn_fwd_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
-                                        _I64, _I64, _I64, _I64, _I64, _I64, _S3,
+    "sage_attn_fwd_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
+                                        _I64, _I64, _I64, _I64, _I64, _I64, _I64, _S3,
                                         ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int, _P, _P]),
     "sage_workspace_bytes_ex": (ctypes.c_size_t, [_I64, _I64, _I64, _I64, _I64]),
     "sage_workspace_layout_ex": (ctypes.c_int, [_I64, _I64, _I64, _I64, _I64, ctypes.POINTER(ctypes.c_size_t)]),
-    "sage_attention_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, ctypes.c_size_t, _I64, _I64, _I64, _I64, _I64,
+    "sage_attention_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, ctypes.c_size_t, _I64, _I64, _I64, _I64, _I64, _I64,
                                          _S3, _S3, _S3, _S3, ctypes.c_int, ctypes.c_int, ctypes.c_int,
-                                         ctypes.c_int, ctypes.c_float, _P]),
+                                         ctypes.c_int, ctypes.c_int, ctypes.c_float, _P]),
     "sage_debug_score_dump": (None, [_P, ctypes.c_int]),
     "sage_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64]),
     "sage_workspace_layout": (ctypes.c_int, [_I64, _I64, _I64, ctypes.POINTER(ctypes.c_size_t)]),

@@ -62,20 +62,19 @@ def strided_view_reason(t: torch.Tensor) -> Optional[str]:
     return None
 
 
-def envelope_reason(q, k, v, tensor_layout, return_lse=False, smooth_v=False, attn_mask=None,
+def envelope_reason(q, k, v, tensor_layout, return_lse=False, attn_mask=None,
                     require_cuda=True) -> Optional[str]:
     """None if the call is inside the envelope, else a short reason (the reference's strings:
-    layout, attn_mask, smooth_v, device, dtype, rank, stride_*, ptr_align, head_dim, batch, heads,
-    seq_len).  head_dim 64 is refused here (the reference falls back for it).  Wider than the
-    reference's hand-written path in three places, following the upstream contract
-    (sageattention/core.py:1081-1101): `return_lse` is served, the query heads may be a multiple of
-    the key/value heads, and the key length may differ from the query length."""
+    layout, attn_mask, device, dtype, rank, stride_*, ptr_align, head_dim, batch, heads,
+    seq_len).  Wider than the reference's hand-written path in four places, following the upstream
+    contract (sageattention/core.py:1081-1101, :1524-1533): `return_lse` is served, the query heads
+    may be a multiple of the key/value heads, the key length may differ from the query length, and
+    head_dim may be any multiple of 8 up to 128 (the quantised codes are zero-filled to 128
+    columns, which is what upstream's host-side padding amounts to)."""
     if tensor_layout not in ("HND", "NHD"):
         return "layout"
     if attn_mask is not None:
         return "attn_mask"
-    if smooth_v:
-        return "smooth_v"
     if require_cuda and not (q.is_cuda and k.is_cuda and v.is_cuda):
         return "device"
     if q.device != k.device or q.device != v.device:
@@ -92,7 +91,7 @@ def envelope_reason(q, k, v, tensor_layout, return_lse=False, smooth_v=False, at
         r = strided_view_reason(t)
         if r is not None:
             return r
-    if q.size(3) != HEAD_DIM or k.size(3) != q.size(3) or v.size(3) != q.size(3):
+    if q.size(3) < 8 or q.size(3) > HEAD_DIM or q.size(3) % 8 or k.size(3) != q.size(3) or v.size(3) != q.size(3):
         return "head_dim"
     if q.size(0) != k.size(0) or q.size(0) != v.size(0):
         return "batch"
@@ -143,6 +142,8 @@ def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool 
     _require_cuda(q, k, v)
     lib = _native.load()
     b, h, n, d = q.shape
+    if d != HEAD_DIM:
+        raise ValueError("the two-step entry points take head_dim 128; use sage_call for smaller heads")
     if int8 is None:
         int8 = q.dtype == torch.float16
     n_pad, bh, dev = pad_len(n), b * h, q.device
@@ -229,10 +230,12 @@ def clear_workspaces():
 
 
 def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=True,
-              int8: Optional[bool] = None, out: Optional[torch.Tensor] = None, return_lse: bool = False):
+              int8: Optional[bool] = None, out: Optional[torch.Tensor] = None, return_lse: bool = False,
+              smooth_v: bool = False):
     """Prologue + attention through the single C entry point `sage_attention_ex`.  Returns a tensor
     with q's shape, dtype and layout -- and, with `return_lse`, also the fp32 log-sum-exp
-    (B, Hq, Nq).  Raises ValueError for a call outside the envelope."""
+    (B, Hq, Nq).  `smooth_v` quantises V minus its sequence mean and adds the mean back to the
+    output.  Raises ValueError for a call outside the envelope."""
     reason = envelope_reason(q, k, v, tensor_layout)
     with _counters_lock:
         _counters["calls"] += 1
@@ -242,7 +245,7 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
         if reason == "device" and not (q.is_cuda and k.is_cuda and v.is_cuda):
             raise ValueError("sageattn (B200 path) needs CUDA tensors; there is no CPU path")
         if reason == "head_dim":
-            raise NotImplementedError("sageattn (B200 path) serves head_dim 128 only")
+            raise NotImplementedError("sageattn (B200 path) serves head_dim 8..128 in multiples of 8")
         raise ValueError("sageattn (B200 path) cannot serve this call: %s" % reason)
     lib = _native.load()
     if tensor_layout == "NHD":
@@ -270,9 +273,9 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     lse = torch.empty((b, h, n), dtype=torch.float32, device=dev) if return_lse else None
     with torch.cuda.device(dev):
         rc = lib.sage_attention_ex(
-            _ptr(ql), _ptr(kl), _ptr(vl), _ptr(ol), _ptr(lse), _ptr(ws), ws.numel(), b, h, hkv, n, nk,
+            _ptr(ql), _ptr(kl), _ptr(vl), _ptr(ol), _ptr(lse), _ptr(ws), ws.numel(), b, h, hkv, n, nk, d,
             _bhr(ql), _bhr(kl), _bhr(vl), _bhr(ol), _dtype_code(q.dtype), qk_mode,
-            1 if is_causal else 0, 1 if smooth_k else 0, float(sm_scale),
+            1 if is_causal else 0, 1 if smooth_k else 0, 1 if smooth_v else 0, float(sm_scale),
             ctypes.c_void_p(int(stream.cuda_stream)))
     _native.check(rc, "sage_attention_ex")
     if return_lse:
@@ -310,8 +313,8 @@ def last_status(q_like: torch.Tensor, b: int, h: int, n: int, hkv: Optional[int]
     dev = q_like.device
     ws = _workspace(dev, int(torch.cuda.current_stream(dev).cuda_stream), b, h, n, hkv, nk)
     lib = _native.load()
-    offs = (ctypes.c_size_t * 12)()
-    if lib.sage_workspace_layout_ex(b, h, h if hkv is None else hkv, n, n if nk is None else nk, offs) != 12:
+    offs = (ctypes.c_size_t * 13)()
+    if lib.sage_workspace_layout_ex(b, h, h if hkv is None else hkv, n, n if nk is None else nk, offs) != 13:
         raise _native.SageNativeError("sage_workspace_layout_ex failed")
     return int(ws[offs[10]: offs[10] + 4].view(torch.int32).item())
 

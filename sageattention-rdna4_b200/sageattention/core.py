@@ -2,11 +2,13 @@
 
 Same names, arguments and error behaviour as the reference's dispatcher for the path this package
 serves (sageattention/core.py:1037-1252 `sageattn`, :1747-1760 `sageattn_qk_int8_pv_fp8_cuda`):
-fp16 / bf16 inputs, head_dim 128, HND or NHD layout, `is_causal`, `sm_scale`, `smooth_k`.
+fp16 / bf16 inputs, head_dim up to 128, HND or NHD layout, `is_causal`, `sm_scale`, `smooth_k`,
+`smooth_v`, `return_lse`, grouped-query heads; plus `sageattn_varlen` (:1444-1558).
 Anything else raises -- there is no second backend to fall back to.
 """
 from __future__ import annotations
 
+import warnings
 from typing import Any, Optional
 
 import torch
@@ -21,8 +23,6 @@ def _reject_common(return_lse: bool, kwargs: dict):
         raise NotImplementedError(
             "sageattention (B200 path) does not implement attn_mask; refusing to ignore it. "
             "Pass mask=None or use a backend that supports masking.")
-    if kwargs.get("smooth_v", False):
-        raise NotImplementedError("sageattention (B200 path) does not implement smooth_v")
 
 
 def sageattn(
@@ -40,16 +40,19 @@ def sageattn(
 ) -> torch.Tensor:
     """Quantised attention: per-token int8 Q.K (e4m3 for bf16 inputs), e4m3 P.V, fp32 softmax.
 
-    q : ``[B, Hq, Nq, 128]`` (``tensor_layout="HND"``) or ``[B, Nq, Hq, 128]`` (``"NHD"``);
+    q : ``[B, Hq, Nq, D]`` (``tensor_layout="HND"``) or ``[B, Nq, Hq, D]`` (``"NHD"``), ``D`` a
+        multiple of 8 up to 128;
     k, v : the same with ``Hkv`` heads and ``Nk`` rows; ``Hq`` a multiple of ``Hkv`` (grouped-query
         attention), ``Nk`` may differ from ``Nq`` when the call is not causal.  float16 or
         bfloat16, one CUDA device; strided views are accepted when the last axis is contiguous and
         every other stride is a multiple of 8 elements.
     return_lse : also return the fp32 log-sum-exp ``[B, Hq, Nq]`` of ``sm_scale * q.k``.
     is_causal : causal mask (query i sees keys <= i).
-    sm_scale : softmax scale, default ``128 ** -0.5``.
+    sm_scale : softmax scale, default ``D ** -0.5``.
     smooth_k (kwarg, default True) : subtract the per-channel sequence mean of K before
         quantising it.
+    smooth_v (kwarg, default False) : quantise V minus its per-channel sequence mean and add the
+        mean back to the output.
     sk1_int8 : ``False`` selects e4m3 Q.K codes for float16 inputs; ``None``/``True`` keep the
         default (int8 for float16).  bfloat16 inputs always use e4m3 codes.
     sk1_backend, sk1_bf16 : accepted for call compatibility; ``False`` asks for a path this
@@ -64,7 +67,7 @@ def sageattn(
         int8 = bool(sk1_int8)
     return _be.sage_call(q, k, v, tensor_layout=tensor_layout, is_causal=bool(is_causal),
                          sm_scale=sm_scale, smooth_k=bool(kwargs.get("smooth_k", True)), int8=int8,
-                         return_lse=bool(return_lse))
+                         return_lse=bool(return_lse), smooth_v=bool(kwargs.get("smooth_v", False)))
 
 
 def sageattn_qk_int8_pv_fp8(
@@ -84,15 +87,74 @@ def sageattn_qk_int8_pv_fp8(
     """The upstream-named entry point (sageattention/core.py:1747-1760 of the reference).  Served
     by the same kernels as `sageattn`: Q and K always get one scale per token (finer than the
     `per_warp` / `per_thread` granularities the argument names), and P.V always accumulates in
-    fp32, so every accepted `pv_accum_dtype` value yields the fp32 behaviour."""
+    fp32, so every accepted `pv_accum_dtype` value yields the fp32 behaviour.  As upstream
+    (:1910-1916), `smooth_v` only takes effect with ``pv_accum_dtype="fp32"`` and is ignored, with
+    a warning, for the two-level accumulators."""
     if qk_quant_gran not in ("per_warp", "per_thread"):
         raise ValueError("qk_quant_gran must be 'per_warp' or 'per_thread'")
     if pv_accum_dtype not in ("fp32", "fp32+fp32", "fp32+fp16"):
         raise ValueError("pv_accum_dtype must be 'fp32', 'fp32+fp32' or 'fp32+fp16'")
-    kwargs = dict(kwargs, smooth_v=smooth_v)
     _reject_common(return_lse, kwargs)
+    if smooth_v and pv_accum_dtype != "fp32":
+        warnings.warn("pv_accum_dtype is '%s', smooth_v will be ignored." % pv_accum_dtype)
+        smooth_v = False
     return _be.sage_call(q, k, v, tensor_layout=tensor_layout, is_causal=bool(is_causal),
-                         sm_scale=sm_scale, smooth_k=bool(smooth_k), int8=None, return_lse=bool(return_lse))
+                         sm_scale=sm_scale, smooth_k=bool(smooth_k), int8=None, return_lse=bool(return_lse),
+                         smooth_v=bool(smooth_v))
+
+
+def sageattn_varlen(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cu_seqlens_q: torch.Tensor,
+    cu_seqlens_k: torch.Tensor,
+    max_seqlen_q: int,
+    max_seqlen_k: int,
+    is_causal: bool = False,
+    sm_scale: Optional[float] = None,
+    smooth_k: bool = True,
+    **kwargs: Any,
+) -> torch.Tensor:
+    """Packed variable-length batch (sageattention/core.py:1444-1558 of the reference).
+
+    q : ``[cu_seqlens_q[-1], Hq, D]``; k, v : ``[cu_seqlens_k[-1], Hkv, D]``; ``cu_seqlens_*`` are
+    int32 / int64 prefix sums of the sequence lengths (``[batch + 1]``).  Returns
+    ``[cu_seqlens_q[-1], Hq, D]``.  Each sequence is one call of the fixed-length kernels on a
+    strided view of the packed tensors (no copies), all on the current stream; the cumulative
+    lengths are read on the host, which synchronises once when they live on the device.
+    `smooth_k` subtracts each sequence's own K mean (the reference subtracts the mean over the
+    whole packed batch; softmax is invariant to either shift, only rounding differs).
+    `max_seqlen_q` / `max_seqlen_k` are checked, not needed.
+    """
+    _reject_common(False, kwargs)
+    if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
+        raise ValueError("sageattn_varlen takes packed [tokens, heads, head_dim] tensors")
+    if cu_seqlens_q.dim() != 1 or cu_seqlens_k.dim() != 1 or cu_seqlens_q.numel() != cu_seqlens_k.numel() \
+            or cu_seqlens_q.numel() < 2:
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must be 1-D with batch + 1 entries each")
+    if cu_seqlens_q.dtype not in (torch.int32, torch.int64) or cu_seqlens_k.dtype not in (torch.int32, torch.int64):
+        raise ValueError("cu_seqlens_q and cu_seqlens_k must be int32 or int64")
+    cq = [int(x) for x in cu_seqlens_q.tolist()]
+    ck = [int(x) for x in cu_seqlens_k.tolist()]
+    if cq[0] != 0 or ck[0] != 0 or cq[-1] != q.size(0) or ck[-1] != k.size(0) or k.size(0) != v.size(0):
+        raise ValueError("cu_seqlens do not match the packed tensors")
+    for i in range(len(cq) - 1):                      # every sequence is checked before anything is launched
+        nq, nk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
+        if nq < 0 or nk < 0 or nq > max_seqlen_q or nk > max_seqlen_k:
+            raise ValueError("sequence %d has lengths (%d, %d) outside 0..max_seqlen" % (i, nq, nk))
+        if nq > 0 and nk == 0:
+            raise ValueError("sequence %d has queries but no keys" % i)
+        if is_causal and nq != nk:
+            raise ValueError("sequence %d: a causal call needs q_len == kv_len" % i)
+    out = torch.empty_like(q)
+    for i in range(len(cq) - 1):
+        if cq[i + 1] == cq[i]:
+            continue
+        _be.sage_call(q[cq[i]:cq[i + 1]].unsqueeze(0), k[ck[i]:ck[i + 1]].unsqueeze(0),
+                      v[ck[i]:ck[i + 1]].unsqueeze(0), tensor_layout="NHD", is_causal=bool(is_causal),
+                      sm_scale=sm_scale, smooth_k=bool(smooth_k), out=out[cq[i]:cq[i + 1]].unsqueeze(0))
+    return out
 
 
 # upstream aliases kept so that existing call sites import unchanged

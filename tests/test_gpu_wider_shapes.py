@@ -91,3 +91,104 @@ def test_nhd_layout_with_grouped_heads_and_lse():
     out_n, lse_n = sageattention.sageattn(qn, kn, vn, tensor_layout="NHD", return_lse=True)
     assert out_n.shape == (2, 200, 4, 128)
     assert torch.equal(out_n.transpose(1, 2), out_h) and torch.equal(lse_n, lse_h)
+
+
+@pytest.mark.parametrize("d", [64, 96, 8, 120])
+@pytest.mark.parametrize("dtype,causal", [(torch.float16, False), (torch.bfloat16, True)])
+def test_head_dim_below_128(d, dtype, causal):
+    g = torch.Generator().manual_seed(5 + d)
+    q = torch.randn(2, 4, 260, d, generator=g).to(dtype)
+    k = (torch.randn(2, 2, 260, d, generator=g) + 0.5).to(dtype)
+    v = torch.randn(2, 2, 260, d, generator=g).to(dtype)
+    out, lse = sageattention.sageattn(q.cuda(), k.cuda(), v.cuda(), is_causal=causal, return_lse=True)
+    assert _status(out, q, k) == 0
+    assert out.shape == q.shape and torch.isfinite(out.float()).all()
+    want, want_l = R.sageattn_oracle(q, k, v, is_causal=causal, tile=128, return_lse=True)
+    ref = R.sdpa_fp32(q, k, v, is_causal=causal)
+    assert R.cosine(out.cpu(), want) >= COS_SAME and R.rel_l1(out.cpu(), want) <= L1_SAME
+    assert R.rel_rms(out.cpu(), ref) < (MAX_REL_RMS if d >= 64 else 0.2)
+    assert (lse.cpu() - want_l).abs().max().item() < 2e-3
+    # identical to the same call on rows zero-padded to 128 columns with the same softmax scale
+    pad = lambda t: torch.nn.functional.pad(t, (0, 128 - d)).cuda()
+    padded = sageattention.sageattn(pad(q), pad(k), pad(v), is_causal=causal, sm_scale=d ** -0.5)
+    assert torch.equal(padded[..., :d], out)
+
+
+def test_head_dim_64_view_of_wider_rows_leaves_neighbours_alone():
+    g = torch.Generator().manual_seed(9)
+    qkv = torch.randn(1, 200, 3, 4, 128, generator=g).half().cuda()       # fused QKV, NHD, only 64 columns used
+    q, k, v = (qkv[:, :, i, :, :64] for i in range(3))
+    out = torch.full((1, 200, 4, 128), 7.0, dtype=torch.float16, device="cuda")
+    be.sage_call(q, k, v, tensor_layout="NHD", out=out[..., :64])
+    torch.cuda.synchronize()
+    assert (out[..., 64:] == 7.0).all()
+    want = sageattention.sageattn(q.contiguous(), k.contiguous(), v.contiguous(), tensor_layout="NHD")
+    assert torch.equal(out[..., :64], want)
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("hq,hkv,nq,nk,causal", [(4, 4, 300, 300, False), (4, 2, 300, 300, True), (4, 2, 100, 515, False)])
+def test_smooth_v(dtype, hq, hkv, nq, nk, causal):
+    g = torch.Generator().manual_seed(6)
+    q = torch.randn(1, hq, nq, 128, generator=g).to(dtype)
+    k = torch.randn(1, hkv, nk, 128, generator=g).to(dtype)
+    v = (torch.randn(1, hkv, nk, 128, generator=g) + 4.0 * torch.randn(1, hkv, 1, 128, generator=g)).to(dtype)
+    out = sageattention.sageattn(q.cuda(), k.cuda(), v.cuda(), is_causal=causal, smooth_v=True)
+    assert _status(out, q, k) == 0
+    want = R.sageattn_oracle(q, k, v, is_causal=causal, tile=128, smooth_v=True)
+    ref = R.sdpa_fp32(q, k, v, is_causal=causal)
+    assert R.cosine(out.cpu(), want) >= COS_SAME and R.rel_l1(out.cpu(), want) <= L1_SAME
+    plain = sageattention.sageattn(q.cuda(), k.cuda(), v.cuda(), is_causal=causal)
+    # a V with a large per-channel offset is exactly the case smooth_v is for
+    assert R.rel_rms(out.cpu(), ref) < 0.6 * R.rel_rms(plain.cpu(), ref)
+    up = sageattention.sageattn_qk_int8_pv_fp8(q.cuda(), k.cuda(), v.cuda(), is_causal=causal, smooth_v=True,
+                                               pv_accum_dtype="fp32")
+    assert torch.equal(up, out)
+    with pytest.warns(UserWarning, match="smooth_v will be ignored"):
+        ign = sageattention.sageattn_qk_int8_pv_fp8(q.cuda(), k.cuda(), v.cuda(), is_causal=causal, smooth_v=True)
+    assert torch.equal(ign, plain)
+
+
+def test_smooth_v_mean_and_codes_match_the_oracle():
+    q, k, v = _inputs(1, 2, 2, 200, 200, torch.float16, 7)
+    v = (v.float() + 2.0).half()
+    out = be.sage_call(q.cuda(), k.cuda(), v.cuda(), smooth_v=True)
+    torch.cuda.synchronize()
+    lib = be._native.load()
+    import ctypes
+    offs = (ctypes.c_size_t * 13)()
+    assert lib.sage_workspace_layout_ex(1, 2, 2, 200, 200, offs) == 13
+    ws = be._workspace(out.device, int(torch.cuda.current_stream().cuda_stream), 1, 2, 200, 2, 200)
+    vmean = ws[offs[12]: offs[12] + 2 * 128 * 4].view(torch.float32).view(1, 2, 128).cpu()
+    v8t = ws[offs[4]: offs[4] + 2 * 256 * 128].view(2, 128, 256).cpu()
+    sv = ws[offs[5]: offs[5] + 2 * 256 * 4].view(torch.float32).view(1, 2, 256).cpu()
+    pq = R.prologue(q, k, v, pad_multiple=128, smooth_v=True)
+    assert torch.equal(vmean, pq["vmean"])
+    assert torch.equal(sv, pq["sv"])
+    want_codes = pq["v8"].to(torch.float8_e4m3fn).view(torch.uint8).view(2, 256, 128).transpose(1, 2)
+    assert torch.equal(v8t, want_codes)
+
+
+@pytest.mark.parametrize("dtype,causal", [(torch.float16, False), (torch.bfloat16, True)])
+def test_varlen_matches_per_sequence_calls(dtype, causal):
+    g = torch.Generator().manual_seed(8)
+    lens_q = [5, 130, 0, 257]
+    lens_k = lens_q if causal else [40, 130, 0, 64]
+    cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
+    cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int64).cuda()
+    q = torch.randn(sum(lens_q), 4, 128, generator=g).to(dtype).cuda()
+    k = torch.randn(sum(lens_k), 2, 128, generator=g).to(dtype).cuda()
+    v = torch.randn(sum(lens_k), 2, 128, generator=g).to(dtype).cuda()
+    out = sageattention.sageattn_varlen(q, k, v, cu_q, cu_k, max(lens_q), max(lens_k), is_causal=causal)
+    assert out.shape == q.shape
+    for i in range(len(lens_q)):
+        a, b = int(cu_q[i]), int(cu_q[i + 1])
+        c, d = int(cu_k[i]), int(cu_k[i + 1])
+        if a == b:
+            continue
+        one = sageattention.sageattn(q[a:b].unsqueeze(0).contiguous(), k[c:d].unsqueeze(0).contiguous(),
+                                     v[c:d].unsqueeze(0).contiguous(), tensor_layout="NHD", is_causal=causal)
+        assert torch.equal(out[a:b], one[0])
+        ref = R.sdpa_fp32(q[a:b].transpose(0, 1).unsqueeze(0).cpu(), k[c:d].transpose(0, 1).unsqueeze(0).cpu(),
+                          v[c:d].transpose(0, 1).unsqueeze(0).cpu(), is_causal=causal)
+        assert R.rel_rms(out[a:b].transpose(0, 1).unsqueeze(0).cpu(), ref) < MAX_REL_RMS

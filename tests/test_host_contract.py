@@ -30,16 +30,19 @@ def test_public_names_and_signature():
     assert up.parameters["pv_accum_dtype"].default == "fp32+fp16"
 
 
-def test_attn_mask_lse_smooth_v_are_refused():
+def test_attn_mask_and_backend_switch_are_refused():
     q = _t(1, 1, 4, 128)
     with pytest.raises(NotImplementedError):
         sageattention.sageattn(q, q, q, attn_mask=torch.ones(4, 4))
     with pytest.raises(ValueError, match="no CPU path"):      # return_lse is served, CPU tensors are not
         sageattention.sageattn(q, q, q, return_lse=True)
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ValueError, match="no CPU path"):      # smooth_v is served too
         sageattention.sageattn(q, q, q, smooth_v=True)
     with pytest.raises(NotImplementedError):
         sageattention.sageattn(q, q, q, sk1_backend=False)
+    with pytest.warns(UserWarning, match="smooth_v will be ignored"):     # upstream rule for two-level accumulators
+        with pytest.raises(ValueError, match="no CPU path"):
+            sageattention.sageattn_qk_int8_pv_fp8(q, q, q, smooth_v=True)
     with pytest.raises(ValueError):
         sageattention.sageattn_qk_int8_pv_fp8(q, q, q, qk_quant_gran="per_block")
 
@@ -79,7 +82,9 @@ def test_accepted_views():
 @pytest.mark.parametrize("mutate,reason", [
     (lambda q, k, v: (q, k, v.float()), "dtype"),
     (lambda q, k, v: (q.float(), k.float(), v.float()), "dtype"),
-    (lambda q, k, v: (q[..., :64], k[..., :64], v[..., :64]), "stride_align"),
+    (lambda q, k, v: (q[..., :64], k[..., :64], v[..., :64]), None),      # head_dim 64 view of wider rows
+    (lambda q, k, v: (q[..., :60], k[..., :60], v[..., :60]), "head_dim"),   # not a multiple of 8
+    (lambda q, k, v: (q[..., :64], k, v), "head_dim"),
     (lambda q, k, v: (q, k[:, :, :8], v), "seq_len"),                     # K and V lengths differ
     (lambda q, k, v: (q, k[:, :, :8], v[:, :, :8]), None),                # a shorter K/V is served
     (lambda q, k, v: (q, k[:, :1], v[:, :1]), None),                      # 2 query heads per K/V head
@@ -90,25 +95,34 @@ def test_accepted_views():
 def test_envelope_reasons(mutate, reason):
     q, k, v = _t(2, 2, 16, 128), _t(2, 2, 16, 128), _t(2, 2, 16, 128)
     q, k, v = mutate(q, k, v)
-    got = be.envelope_reason(q, k, v, "HND", require_cuda=False)
-    if reason == "stride_align":
-        # a D=64 slice of a D=128 tensor keeps a 128-element row stride: it passes the stride rule
-        # and is refused for its head_dim
-        assert got == "head_dim"
-    else:
-        assert got == reason
+    assert be.envelope_reason(q, k, v, "HND", require_cuda=False) == reason
 
 
 def test_envelope_layout_and_flags():
     q = _t(1, 1, 4, 128)
     assert be.envelope_reason(q, q, q, "HDN", require_cuda=False) == "layout"
     assert be.envelope_reason(q, q, q, "HND", return_lse=True, require_cuda=False) is None
-    assert be.envelope_reason(q, q, q, "HND", smooth_v=True, require_cuda=False) == "smooth_v"
     assert be.envelope_reason(q, q, q, "HND", attn_mask=q, require_cuda=False) == "attn_mask"
     assert be.envelope_reason(q, q, q, "HND", require_cuda=True) == "device"
     assert be.envelope_reason(q, q, q, "NHD", require_cuda=False) is None
-    d64 = _t(1, 1, 4, 64)
-    assert be.envelope_reason(d64, d64, d64, "HND", require_cuda=False) == "head_dim"
+    d64, d136 = _t(1, 1, 4, 64), _t(1, 1, 4, 136)
+    assert be.envelope_reason(d64, d64, d64, "HND", require_cuda=False) is None
+    assert be.envelope_reason(d136, d136, d136, "HND", require_cuda=False) == "head_dim"
+
+
+def test_varlen_argument_checks():
+    q = _t(10, 2, 128)
+    cu = torch.tensor([0, 4, 10], dtype=torch.int32)
+    with pytest.raises(ValueError, match="packed"):
+        sageattention.sageattn_varlen(q.unsqueeze(0), q, q, cu, cu, 6, 6)
+    with pytest.raises(ValueError, match="int32 or int64"):
+        sageattention.sageattn_varlen(q, q, q, cu.float(), cu, 6, 6)
+    with pytest.raises(ValueError, match="do not match"):
+        sageattention.sageattn_varlen(q, q, q, torch.tensor([0, 4, 9]), cu, 6, 6)
+    with pytest.raises(ValueError, match="max_seqlen"):
+        sageattention.sageattn_varlen(q, q, q, cu, cu, 5, 6)
+    with pytest.raises(ValueError, match="no CPU path"):
+        sageattention.sageattn_varlen(q, q, q, cu, cu, 6, 6)
 
 
 def test_pad_len():
