@@ -192,6 +192,28 @@ def other_arms(q, k, v, dev, causal_main: bool) -> dict:
         med = statistics.median(samples)
         short[str(n)] = dict(ms=med, tflops=4.0 * H * n * n * D / (med * 1e-3) / 1e12)
     out["short_calls_fp16_non_causal_wall_clock"] = short
+    # call shapes beyond the reference's hand-written envelope, same H and N as the headline
+    n = q.shape[2]
+    wide = {}
+    ms = timed(lambda: sageattention.sageattn(q, k, v, is_causal=causal_main, return_lse=True), 3)
+    wide["return_lse"] = dict(ms=ms, tflops=flops(causal_main) / (ms * 1e-3) / 1e12)
+    ms = timed(lambda: sageattention.sageattn(q, k, v, is_causal=causal_main, smooth_v=True), 3)
+    wide["smooth_v"] = dict(ms=ms, tflops=flops(causal_main) / (ms * 1e-3) / 1e12)
+    kg, vg = k[:, :8].contiguous(), v[:, :8].contiguous()
+    ms = timed(lambda: sageattention.sageattn(q, kg, vg, is_causal=causal_main), 3)
+    wide["grouped_query_48q_8kv"] = dict(ms=ms, tflops=flops(causal_main) / (ms * 1e-3) / 1e12)
+    q64, k64, v64 = (t[..., :64].contiguous() for t in (q, k, v))
+    ms = timed(lambda: sageattention.sageattn(q64, k64, v64, is_causal=causal_main), 3)
+    wide["head_dim_64"] = dict(ms=ms, tflops=0.5 * flops(causal_main) / (ms * 1e-3) / 1e12,
+                               note="flops counted at head_dim 64; the codes are zero-filled to 128 columns")
+    del q64, k64, v64, kg, vg
+    seqs, ln = 11, 4096                                  # packed batch of 11 sequences of 4096 tokens
+    qv, kv, vv = (t[0, :, :seqs * ln].transpose(0, 1).contiguous() for t in (q, k, v))
+    cu = torch.arange(0, (seqs + 1) * ln, ln, dtype=torch.int32)
+    ms = timed(lambda: sageattention.sageattn_varlen(qv, kv, vv, cu, cu, ln, ln, is_causal=causal_main), 3)
+    wide["varlen_11x4096"] = dict(ms=ms, tflops=seqs * 4.0 * H * ln * ln * D * (0.5 if causal_main else 1.0)
+                                  / (ms * 1e-3) / 1e12)
+    out["wider_call_shapes"] = wide
     return out
 
 
