@@ -34,6 +34,8 @@
 namespace sage {
 
 constexpr int ATT_THREADS = 384;                    // 3 warpgroups: {TMA, MMA, 2 idle warps}, 2 x softmax
+constexpr int REGS_AT_LAUNCH = 80;                  // what __launch_bounds__(384, 2) yields
+constexpr int REGS_PRODUCER = 32, REGS_SOFTMAX = 104;   // after setmaxnreg
 constexpr uint32_t TILE_BYTES = TILE * HD;          // 16 KiB: 128 rows x 128 one-byte codes
 constexpr uint32_t VEC_BYTES = TILE * 4;            // 128 floats
 constexpr uint32_t OFF_Q = 0;
@@ -338,10 +340,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const bool skip_all = misc[1] != 0u;
 
   // Registers move from the producer/MMA warpgroup to the two softmax warpgroups:
-  // 384 x 80 at launch = 128 x 32 + 256 x 104 afterwards.
+  // 384 x 80 at launch = 128 x 32 + 256 x 104 afterwards.  setmaxnreg.inc blocks until the pool
+  // holds the registers it asks for, so the two sides must never add up to more than the launch
+  // allocation (80 per thread: 65536 / (384 x 2 CTAs) rounded down to a multiple of 8).
+  static_assert(128 * REGS_PRODUCER + 256 * REGS_SOFTMAX <= ATT_THREADS * REGS_AT_LAUNCH,
+                "setmaxnreg.inc would wait for registers that never become free");
   if (!skip_all) {
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 32;");
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_PRODUCER));
     }
     if (warp == 0) {
       // ------------------------------- TMA producer -------------------------------
@@ -403,7 +409,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     } else if (warp >= 4) {
       // ------------------------------- softmax warps ------------------------------
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 104;");
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
       const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
       const int half = (warp - 4) >> 2;                     // which 64 key columns of the tile
       const int row = 32 * quarter + lane;                  // TMEM lane == query row of the tile
@@ -682,6 +688,12 @@ static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, con
   if (dev < 0 || dev >= 64 || !opted_in[dev]) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
     if (e != cudaSuccess) return e;
+    // The register hand-over inside the kernel assumes the allocation the compiler reported; a
+    // build that came out with fewer registers per thread would leave setmaxnreg.inc waiting.
+    cudaFuncAttributes attr;
+    e = cudaFuncGetAttributes(&attr, kern);
+    if (e != cudaSuccess) return e;
+    if (attr.numRegs * ATT_THREADS < 128 * REGS_PRODUCER + 256 * REGS_SOFTMAX) return cudaErrorLaunchOutOfResources;
     if (dev >= 0 && dev < 64) opted_in[dev] = true;
   }
   kern<<<grid, ATT_THREADS, SMEM_BYTES, st>>>(mq, mk, mv, ka);
