@@ -40,7 +40,12 @@ def sageattn_sharded(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, is_causa
     (1, units, N, 128) in HND layout (use `partition_units` to slice a replicated tensor).  With
     `gather=False` (the hot path) the local output is returned and nothing is communicated; with
     `gather=True` the outputs of all ranks are all-gathered along the unit axis and every rank
-    returns (1, total_units, N, 128).  `attn_fn` defaults to `sageattn`."""
+    returns (1, total_units, N, 128).  `attn_fn` defaults to `sageattn`.
+
+    With grouped-query heads, partition the key/value units and give each rank the matching
+    `g = Hq / Hkv` times as many query units: q is (1, g*units, Nq, D), k and v are
+    (1, units, Nk, D); query unit u reads key/value unit u // g, so a contiguous range of
+    key/value units [a, b) goes with the query range [g*a, g*b)."""
     if attn_fn is None:
         from .core import sageattn as attn_fn
     out = attn_fn(q, k, v, tensor_layout="HND", is_causal=is_causal, sm_scale=sm_scale,

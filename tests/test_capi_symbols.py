@@ -54,3 +54,40 @@ def test_argument_errors_are_reported_before_any_launch():
     assert rc == _native.SAGE_E_ARG
     with pytest.raises(ValueError):
         _native.check(rc, "sage_attn_fwd")
+
+
+def test_extended_entry_points_validate_on_the_host():
+    """The `_ex` entry points refuse bad shapes with a code and a message before touching CUDA."""
+    lib = _native.load()
+    s3 = _native.strides3(1024, 512, 128)
+    buf = (ctypes.c_char * 4096)()                       # host memory: every call below must stop at validation
+    p = ctypes.c_void_p((ctypes.addressof(buf) + 255) // 256 * 256)
+    # sizes: the workspace does not depend on head_dim; bad head counts give 0 / an error
+    assert lib.sage_workspace_bytes_ex(1, 8, 2, 300, 500) > lib.sage_workspace_bytes_ex(1, 8, 2, 300, 100)
+    assert lib.sage_workspace_bytes_ex(1, 8, 3, 300, 300) == 0          # 8 is not a multiple of 3
+    assert lib.sage_workspace_bytes_ex(1, 4, 4, 300, 300) >= lib.sage_workspace_bytes(1, 4, 300)
+    offs = (ctypes.c_size_t * 13)()
+    assert lib.sage_workspace_layout_ex(2, 4, 2, 70, 200, offs) == 13
+    vals = list(offs)
+    assert vals == sorted(vals) and all(v % 256 == 0 for v in vals)
+    assert lib.sage_workspace_layout_ex(2, 4, 3, 70, 200, offs) == _native.SAGE_E_ARG
+
+    def attention(hq, hkv, nq, nk, d, causal=0, ws=p, ws_bytes=1 << 40):
+        return lib.sage_attention_ex(p, p, p, p, None, ws, ws_bytes, 1, hq, hkv, nq, nk, d,
+                                     s3, s3, s3, s3, 0, -1, causal, 1, 0, 0.1, None)
+
+    for d in (0, 4, 12, 136, 256):
+        assert attention(2, 2, 16, 16, d) == _native.SAGE_E_UNSUPPORTED
+        assert b"head_dim" in lib.sage_last_error()
+    assert attention(3, 2, 16, 16, 128) == _native.SAGE_E_ARG
+    assert b"multiple" in lib.sage_last_error()
+    assert attention(2, 2, 0, 16, 128) == _native.SAGE_E_ARG
+    assert attention(2, 2, 16, 16, 128, ws=None) == _native.SAGE_E_ARG
+    assert attention(2, 2, 16, 16, 128, ws_bytes=1024) == _native.SAGE_E_WORKSPACE
+    assert b"needs" in lib.sage_last_error()
+    assert attention(70000, 70000, 16, 16, 128) == _native.SAGE_E_UNSUPPORTED   # grid limit
+    # the two-step forms
+    rc = lib.sage_prologue_ex(*([None] * 15), 1, 2, 2, 16, 16, 128, 64, s3, s3, s3, 0, 0, 1, None)
+    assert rc == _native.SAGE_E_ARG and b"null" in lib.sage_last_error()
+    rc = lib.sage_prologue_ex(*([p] * 15), 1, 2, 2, 16, 16, 256, 64, s3, s3, s3, 0, 0, 1, None)
+    assert rc == _native.SAGE_E_ARG and b"padded key length" in lib.sage_last_error()

@@ -33,6 +33,9 @@ def _free_port():
 
 def _fake_attn(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=True):
     # stands in for the CUDA call on CPU ranks: exact softmax attention per unit
+    if k.shape[1] != q.shape[1]:                       # grouped-query heads
+        g = q.shape[1] // k.shape[1]
+        k, v = k.repeat_interleave(g, dim=1), v.repeat_interleave(g, dim=1)
     return torch.nn.functional.scaled_dot_product_attention(
         q.float(), k.float(), v.float(), is_causal=is_causal).to(q.dtype)
 
@@ -52,6 +55,11 @@ def _worker(rank, world, port, units, ret):
         assert full.shape == want.shape
         assert torch.equal(full, want)
         assert torch.equal(gather_units(local), want)
+        # grouped-query heads: key/value units are partitioned, each carries `grp` query units
+        grp = 2
+        qg = torch.randn(1, grp * units, 24, 128, generator=g).half()
+        out = sageattn_sharded(qg[:, grp * lo:grp * hi], k[:, lo:hi], v[:, lo:hi], gather=True, attn_fn=_fake_attn)
+        assert torch.equal(out, _fake_attn(qg, k, v))
         ret[rank] = True
     finally:
         dist.destroy_process_group()
