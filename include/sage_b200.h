@@ -67,9 +67,12 @@ size_t sage_prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
  *   svp       (B*H, N_pad)       fp32 staged factor  fl(fl(sv / S) * 448)
  *   s_fold    (B*H)              S = max(max_n sv, 1)
  *   mean      (B*H, 128)         fp32 sequence mean of K (written only when smooth_k != 0)
- *   ctrl      sage_prologue_ctrl_bytes() of scratch; contents need not be initialised
+ *   ctrl      sage_prologue_ctrl_bytes() of scratch; contents need not be initialised.  After the
+ *             call its 32-bit word number 4*B*H is non-zero if a bounded wait inside the quantiser
+ *             ran out (the outputs are then undefined); sage_attention reports the same event as
+ *             bit 8 of its status word
  *   N_pad     must equal sage_pad_len(N)
- * Two kernel launches (mean, quantise) and one small memset. */
+ * Three kernel launches (mean, quantise, fold of S and svp) and one small memset. */
 int sage_prologue(const void* q, const void* k, const void* v,
                   void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
                   float* s_fold, float* mean, void* ctrl,

@@ -118,7 +118,8 @@ int prologue_impl(const void* q, const void* k, const void* v,
                   void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
                   float* s_fold, float* mean, float* qm, float* vmean, void* ctrl, const Dims& d, int64_t Nk_pad,
                   const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
-                  int dtype, int qk_mode, int smooth_k, void* stream, const char* who) {
+                  int dtype, int qk_mode, int smooth_k, void* stream, const char* who,
+                  int32_t* status = nullptr) {
   g_err[0] = 0;
   int rc = check_dims(d);
   if (rc) return rc;
@@ -136,7 +137,7 @@ int prologue_impl(const void* q, const void* k, const void* v,
     return fail(SAGE_E_ARG, "%s: pointers must be 16-byte aligned", who);
   sage::PrologueParams p;
   p.q = q; p.k = k; p.v = v; p.q8 = q8; p.k8 = k8; p.v8t = v8t;
-  p.sq = sq; p.sk = sk; p.sv = sv; p.svp = svp; p.s_fold = s_fold; p.mean = mean; p.ctrl = ctrl; p.qm = qm; p.vmean = vmean;
+  p.sq = sq; p.sk = sk; p.sv = sv; p.svp = svp; p.s_fold = s_fold; p.mean = mean; p.ctrl = ctrl; p.qm = qm; p.vmean = vmean; p.status = status;
   p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq; p.D = d.D;
   for (int i = 0; i < 3; ++i) { p.q_strides[i] = q_strides[i]; p.k_strides[i] = k_strides[i]; p.v_strides[i] = v_strides[i]; }
   p.dtype = dtype; p.qk_mode = qk_mode; p.smooth_k = smooth_k;
@@ -202,7 +203,7 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
                      reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.sv),
                      reinterpret_cast<float*>(w + L.svp), reinterpret_cast<float*>(w + L.s_fold),
                      reinterpret_cast<float*>(w + L.mean), qm, vmean, w + L.ctrl, d, Nk_pad,
-                     q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, who);
+                     q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, who, status);
   if (rc) return rc;
   return attn_impl(w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
                    reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.svp),

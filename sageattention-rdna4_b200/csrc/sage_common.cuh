@@ -18,11 +18,13 @@ constexpr float LOG2E_F = 1.4426950408889634f;
 
 // Control block of the prologue (device memory, zeroed by a memset at the start of every call).
 struct CtrlHeader {
-  // per head: [0] arrivals of the K mean kernel, [1] arrivals of the quantiser, [2] max V scale
-  // bits, [3] arrivals of the V mean kernel (smooth_v), laid out as four arrays of BH words; the
-  // fp64 partial sums (shared by the two mean launches, which run one after the other) follow at
-  // `partial_off`.
-  static __host__ __device__ inline size_t words(int64_t bh) { return (size_t)4 * (size_t)bh; }
+  // per head: [0] arrivals of the K mean kernel, [1] unused, [2] max V scale bits, [3] arrivals
+  // of the V mean kernel (smooth_v), laid out as four arrays of BH words; then one status word
+  // (non-zero when a wait inside the quantiser ran out), one pad word and the quantiser's 64-bit
+  // work counter; the fp64 partial sums (shared by the two mean launches, which run one after the
+  // other) follow at `partial_off`.
+  static __host__ __device__ inline size_t words(int64_t bh) { return (size_t)4 * (size_t)bh + 4; }
+  static __host__ __device__ inline size_t status_word(int64_t bh) { return (size_t)4 * (size_t)bh; }
   static __host__ __device__ inline size_t partial_off(int64_t bh) {
     return (words(bh) * 4 + 255) / 256 * 256;
   }

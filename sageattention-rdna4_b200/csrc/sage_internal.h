@@ -13,6 +13,7 @@ struct PrologueParams {
   void* ctrl;
   float* qm;                                           // optional (B*Hq, Nq): q . K-mean, for the LSE
   float* vmean;                                        // optional (B*H, 128): smooth_v subtracts the sequence mean of V
+  int32_t* status;                                     // optional: receives bit 8 if a wait on a tile load ran out
   int64_t B, H, N, N_pad;                              // K/V side: heads, keys, padded keys
   int64_t Hq, Nq;                                      // query side (Hq a multiple of H)
   int64_t D;                                           // head_dim of q/k/v rows (multiple of 8, <= 128); codes are 128 wide, zero-filled

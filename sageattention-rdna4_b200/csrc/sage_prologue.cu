@@ -1,6 +1,7 @@
-// Quantisation prologue for B200: sequence mean of K (smooth_k), then one pass over a 128-token
-// tile of Q, K and V that writes the int8 / e4m3 codes, the per-token scales, V transposed, and
-// the per-head fold S with its staged factor.
+// Quantisation prologue for B200: sequence mean of K (smooth_k; of V too with smooth_v), then one
+// persistent, TMA-fed pass over the 128-token tiles of K, V and Q that writes the int8 / e4m3
+// codes, the per-token scales and V transposed, then a small kernel that folds the per-head S and
+// its staged factor.
 //
 // Arithmetic contract (reference: kernels/hip/h34_prologue.hip:116-211,259-282;
 // kernels/hip/sk1_t6i.hip:104-117; kernels/hip/sk1_t4a1sb.hip:89-100;
@@ -15,9 +16,14 @@
 //           e4m3 arm: code = e4m3(clamp(q * (448/amax), +-448)); scale = amax/448
 //   pad   : K8 = 0, SK = 1, V8T = 0, SV = 0
 //   S     = max(max_n sv, 1); SVP = fl(fl(sv / S) * 448)
+// The clamps to +-448 are done by the saturating e4m3 conversion (same codes).
 // The fp64 mean is summed in a different (wider) order than the reference's eight strided
 // partials; both are exact, hence identical, whenever the fp64 partial sums are exact, which holds
 // for fp16 data when sum|K| < 2^29 per channel and for bf16 data of ordinary dynamic range.
+#include <cuda.h>
+
+#include <type_traits>
+
 #include "sage_common.cuh"
 #include "sage_internal.h"
 
@@ -75,12 +81,6 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
 }
 
 // ------------------------------------------------------------------------------------------------
-// Kernel 2: quantise one 128-token tile of ONE of Q, K, V.  grid (N_pad/128, B*H, 3), block 256,
-// four CTAs per SM.  blockIdx.z selects the tensor, so CTAs in different phases (load, convert,
-// store) share an SM and keep the memory system busy.
-// Thread (c = tid & 15, r0 = tid >> 4) owns columns 8c..8c+7 of rows r0, r0+16, ..., r0+112, so a
-// half-warp reads one 256-byte row with 16-byte loads and the row absmax is four shuffles.
-//
 // Division.  K and V are divided by their scale with an IEEE-correct quotient obtained as
 //   rc = rn(1/s) (correctly rounded);  q0 = rn(x*rc);  r = x - q0*s (one fma, exact);  q = fma(r, rc, q0)
 // which equals rn(x/s) whenever rc is the correctly rounded reciprocal and nothing over/underflows
@@ -90,38 +90,20 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
 // even, the low byte of the sum is the two's-complement code; |x/s| <= 127 needs no clamp.
 // ------------------------------------------------------------------------------------------------
 struct QuantArgs {
-  const void *q, *k, *v;
   uint8_t *q8, *k8, *v8t;
-  float *sq, *sk, *sv, *svp, *s_fold;
+  float *sq, *sk, *sv;
   const float* mean;
   const float* vmean;             // optional: sequence mean of V, subtracted before quantising (smooth_v)
-  unsigned *arrivals, *svmax_bits;
+  unsigned* svmax_bits;           // per K/V head: running maximum of the V scales, as float bits
   long long N, N_pad, H;          // keys: length, padded length, K/V heads per batch element
   long long Nq, Hq, group;        // queries: length, heads per batch element, Hq / H (1 without GQA)
   long long BHq, BHkv;            // B*Hq, B*H
   float* qm;                      // optional (B*Hq, Nq): dot(q row, K mean of its K/V head), for the LSE
-  long long q_sb, q_sh, q_sr, k_sb, k_sh, k_sr, v_sb, v_sh, v_sr;
   int sub_mean;
-  int D;                          // head_dim of the q/k/v rows; code columns D..127 are zero
+  int32_t* status;                // set non-zero when a wait on a tile load ran out
+  int32_t* status2;               // optional second word that receives the same report
+  unsigned long long* next_item;  // global work counter (zeroed with the control block)
 };
-
-__device__ __forceinline__ float half_warp_max(float x) {
-  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 8));
-  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 4));
-  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
-  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
-  return x;
-}
-
-template <typename T>
-__device__ __forceinline__ void load_rows(const T* base, long long sr, long long n_base, int r0,
-                                          long long N, bool col_live, uint4* raw) {
-#pragma unroll
-  for (int i = 0; i < 8; ++i) {
-    const long long n = n_base + r0 + 16 * i;
-    raw[i] = (n < N && col_live) ? __ldg(reinterpret_cast<const uint4*>(base + n * sr)) : make_uint4(0, 0, 0, 0);
-  }
-}
 
 // rn(x / s) given rc = rn(1/s)
 __device__ __forceinline__ float div_by_scale(float x, float s, float rc) {
@@ -129,224 +111,375 @@ __device__ __forceinline__ float div_by_scale(float x, float s, float rc) {
   const float r = -__fmaf_rn(q0, s, -x);      // x - q0*s, written so that a zero keeps x's sign
   return __fmaf_rn(r, rc, q0);
 }
-// round-half-even of |y| < 2^22 to an int8 code, four per word (a in the low byte)
-__device__ __forceinline__ uint32_t i8x4_magic(float a, float b, float c, float d) {
-  const uint32_t ua = __float_as_uint(__fadd_rn(a, 12582912.0f)), ub = __float_as_uint(__fadd_rn(b, 12582912.0f));
-  const uint32_t uc = __float_as_uint(__fadd_rn(c, 12582912.0f)), ud = __float_as_uint(__fadd_rn(d, 12582912.0f));
-  return __byte_perm(__byte_perm(ua, ub, 0x0040), __byte_perm(uc, ud, 0x0040), 0x5410);
+
+// ------------------------------------------------------------------------------------------------
+// Kernel 2: persistent CTAs (three per SM) draw 128-token tiles of K, V and Q from one global work
+// counter; thread 0 keeps the next tile's 32 KB tensor-map load in flight into a shared-memory
+// ring while the 256 threads quantise the tile that has landed.  Out-of-range rows and, for
+// head_dim < 128, out-of-range columns arrive as zeros from the tensor map.
+// Thread (c = tid & 7, r0 = tid >> 3) owns columns 8c..8c+7 and 64+8c..64+8c+7 of rows r0, r0+32,
+// r0+64, r0+96: a quarter-warp reads one 256-byte row with two conflict-free 16-byte loads and the
+// row maximum is three shuffles.
+// ------------------------------------------------------------------------------------------------
+constexpr int QT_STAGES = 2;        // shared-memory ring: one tile being quantised, one in flight
+constexpr int QT_MINBLOCKS = 3;     // CTAs per SM (3 x 64 KB of shared memory, 80 registers per thread)
+constexpr uint32_t QT_STAGE_BYTES = TILE * HD * 2;
+constexpr uint32_t QT_SMEM_BYTES = QT_STAGES * QT_STAGE_BYTES + 128 /* alignment slack */ + 64 /* barriers */;
+constexpr long long QT_WAIT_CYCLES = 4000000000LL;
+
+__device__ __forceinline__ uint32_t qt_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ uint32_t qt_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+               : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok;
+}
+__device__ __forceinline__ float quarter_warp_max(float x) {
+  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 4));
+  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 2));
+  x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, 1));
+  return x;
+}
+// rn(a / d) for a compile-time divisor: rc = rn(1/d) is a constant, the rest is Markstein's sequence
+// (checked against true division over every mantissa of several binades for d = 127 and 448).
+template <int DIV>
+__device__ __forceinline__ float div_const(float a) {
+  constexpr float d = (float)DIV, rc = 1.0f / (float)DIV;
+  const float q0 = __fmul_rn(a, rc);
+  const float r = __fmaf_rn(-q0, d, a);
+  return __fmaf_rn(r, rc, q0);
+}
+__device__ __forceinline__ uint32_t i8x4_magic2(float2 ab, float2 cd) {
+  const float2 m = make_float2(12582912.0f, 12582912.0f);
+  const float2 u = __fadd2_rn(ab, m), v = __fadd2_rn(cd, m);
+  return __byte_perm(__byte_perm(__float_as_uint(u.x), __float_as_uint(u.y), 0x0040),
+                     __byte_perm(__float_as_uint(v.x), __float_as_uint(v.y), 0x0040), 0x5410);
 }
 
 template <typename T, bool INT8>
-__global__ void __launch_bounds__(256, 4)
-quant_qkv_kernel(const QuantArgs a) {
-  __shared__ __align__(16) uint32_t vt[TILE * 32];   // e4m3 V tile, [token][32 words], XOR-swizzled
-  __shared__ float s_wmax[8];
-  __shared__ int s_last;
+__global__ void __launch_bounds__(256, QT_MINBLOCKS)
+quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                     const __grid_constant__ CUtensorMap tm_v, const QuantArgs a) {
+  extern __shared__ uint8_t qt_smem[];
+  __shared__ long long s_item[QT_STAGES];
   constexpr float QMAX = INT8 ? I8_MAX : F8_MAX;
+  constexpr int QDIV = INT8 ? 127 : 448;
 
-  const int tid = threadIdx.x, c = tid & 15, r0 = tid >> 4, lane = tid & 31, warp = tid >> 5;
-  const int bh = gridDim.y - 1 - blockIdx.y;         // last heads first: their K is still in L2 after the mean pass
-  const int which = blockIdx.z == 0 ? 1 : (blockIdx.z == 1 ? 0 : 2);   // 0 Q, 1 K, 2 V; K tiles are issued first
-  const long long n_base = (long long)blockIdx.x * TILE;
-  uint4 raw[8];
-  const bool col_live = 8 * c < a.D;
+  const uint32_t raw_addr = qt_smem_u32(qt_smem);
+  const uint32_t base = (raw_addr + 127u) & ~127u;
+  uint8_t* gbase = qt_smem + (base - raw_addr);
+  const uint32_t bar0 = base + QT_STAGES * QT_STAGE_BYTES;
+  const int tid = threadIdx.x, c = tid & 7, r0 = tid >> 3, lane = tid & 31, warp = tid >> 5;
 
-  if (which == 0) {
-    // ---------------------------------- Q ----------------------------------
-    const long long N = a.Nq;
-    if (bh >= a.BHq || n_base >= N) return;
-    const long long b = bh / a.Hq, h = bh - b * a.Hq;
-    const T* qb = reinterpret_cast<const T*>(a.q) + b * a.q_sb + h * a.q_sh + 8 * c;
-    load_rows<T>(qb, a.q_sr, n_base, r0, N, col_live, raw);
-    float mu[8];
-    if (a.qm != nullptr) {                            // the K mean of this query head's K/V head
-      const long long bh_kv = b * a.H + h / a.group;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) mu[e] = a.mean[(size_t)bh_kv * HD + 8 * c + e];
+  const long long tiles_q = (a.Nq + TILE - 1) / TILE, tiles_k = a.N_pad / TILE;
+  const long long items_k = a.BHkv * tiles_k, items_q = a.BHq * tiles_q;
+  const long long total = 2 * items_k + items_q;
+
+  // item -> (tensor, head, tile): K first with the last heads first (their rows are still in L2
+  // after the mean pass), then V (so that the per-head folds overlap the Q items), then Q
+  auto decode = [&](long long it, int& which, long long& bh, long long& tile) {
+    if (it < items_k) { which = 1; bh = a.BHkv - 1 - it / tiles_k; tile = it % tiles_k; }
+    else if (it < 2 * items_k) { const long long j = it - items_k; which = 2; bh = a.BHkv - 1 - j / tiles_k; tile = j % tiles_k; }
+    else { const long long j = it - 2 * items_k; which = 0; bh = a.BHq - 1 - j / tiles_q; tile = j % tiles_q; }
+  };
+  // Items are handed out through one global counter: a CTA that is held up (by a head's fold, say)
+  // simply takes fewer of them.  Thread 0 draws the item for a stage, publishes it in s_item and
+  // starts its load; past the end it publishes -1 and completes the stage's barrier by hand.
+  auto issue = [&](int stage) {
+    const long long it = (long long)atomicAdd(a.next_item, 1ULL);
+    const uint32_t bar_ = bar0 + 8u * (uint32_t)stage;
+    if (it >= total) {
+      s_item[stage] = -1;
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_) : "memory");
+      return;
     }
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const long long n = n_base + r0 + 16 * i;
-      float x[8];
-      unpack8<T>(raw[i], x);
-      float amax = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) amax = fmaxf(amax, fabsf(x[e]));
-      amax = fmaxf(half_warp_max(amax), SCALE_FLOOR);
-      const float qinv = __fdiv_rn(QMAX, amax);
-      float y[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = __fmul_rn(x[e], qinv);
-      uint2 w;
-      if (INT8) {
-        w.x = i8x4_magic(y[0], y[1], y[2], y[3]);
-        w.y = i8x4_magic(y[4], y[5], y[6], y[7]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = fminf(fmaxf(y[e], -F8_MAX), F8_MAX);
-        w.x = e4m3x4(y[0], y[1], y[2], y[3]);
-        w.y = e4m3x4(y[4], y[5], y[6], y[7]);
-      }
-      if (n < N) {
-        *reinterpret_cast<uint2*>(a.q8 + ((size_t)bh * N + n) * HD + 8 * c) = w;
-        if (c == 0) a.sq[(size_t)bh * N + n] = __fdiv_rn(amax, QMAX);
-      }
-      if (a.qm != nullptr) {                          // fixed-order fp32 dot product of the raw row
-        float d = 0.f;
-#pragma unroll
-        for (int e = 0; e < 8; ++e) d = __fmaf_rn(x[e], mu[e], d);
-        d += __shfl_xor_sync(0xffffffffu, d, 8);
-        d += __shfl_xor_sync(0xffffffffu, d, 4);
-        d += __shfl_xor_sync(0xffffffffu, d, 2);
-        d += __shfl_xor_sync(0xffffffffu, d, 1);
-        if (c == 0 && n < N) a.qm[(size_t)bh * N + n] = d;
-      }
-    }
-    return;
+    s_item[stage] = it;
+    int which; long long bh, tile;
+    decode(it, which, bh, tile);
+    const long long heads = (which == 0) ? a.Hq : a.H;
+    const int b = (int)(bh / heads), h = (int)(bh - (long long)b * heads);
+    const CUtensorMap* map = (which == 0) ? &tm_q : (which == 1 ? &tm_k : &tm_v);
+    const uint32_t bar = bar0 + 8u * (uint32_t)stage, dst = base + (uint32_t)stage * QT_STAGE_BYTES;
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(QT_STAGE_BYTES) : "memory");
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"((int)(tile * TILE)), "r"(h), "r"(b) : "memory");
+  };
+
+  if (tid == 0) {
+    for (int s = 0; s < QT_STAGES; ++s)
+      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar0 + 8u * (uint32_t)s), "r"(1u) : "memory");
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
-
-  const long long N = a.N, N_pad = a.N_pad;
-  if (bh >= a.BHkv || n_base >= N_pad) return;
-  const long long b = bh / a.H, h = bh - b * a.H;
-
-  if (which == 1) {
-    // ---------------------------------- K ----------------------------------
-    const T* kb = reinterpret_cast<const T*>(a.k) + b * a.k_sb + h * a.k_sh + 8 * c;
-    load_rows<T>(kb, a.k_sr, n_base, r0, N, col_live, raw);
-    float mu[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) mu[e] = a.sub_mean ? a.mean[(size_t)bh * HD + 8 * c + e] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const long long n = n_base + r0 + 16 * i;
-      const bool live = n < N;
-      float x[8];
-      unpack8<T>(raw[i], x);
-      float amax = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        x[e] = (live && col_live) ? __fsub_rn(x[e], mu[e]) : 0.f;
-        amax = fmaxf(amax, fabsf(x[e]));
-      }
-      amax = half_warp_max(amax);
-      const float sk = fmaxf(__fdiv_rn(amax, QMAX), SCALE_FLOOR);
-      const float rc = __frcp_rn(sk);
-      float y[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = div_by_scale(x[e], sk, rc);
-      uint2 w;
-      if (INT8) {
-        w.x = i8x4_magic(y[0], y[1], y[2], y[3]);
-        w.y = i8x4_magic(y[4], y[5], y[6], y[7]);
-      } else {
-#pragma unroll
-        for (int e = 0; e < 8; ++e) y[e] = fminf(y[e], F8_MAX);
-        w.x = e4m3x4(y[0], y[1], y[2], y[3]);
-        w.y = e4m3x4(y[4], y[5], y[6], y[7]);
-      }
-      *reinterpret_cast<uint2*>(a.k8 + ((size_t)bh * N_pad + n) * HD + 8 * c) = w;
-      if (c == 0) a.sk[(size_t)bh * N_pad + n] = live ? sk : 1.0f;
-    }
-    return;
-  }
-
-  // ---------------------------------- V ----------------------------------
-  float svmax = 0.f;
-  {
-    const T* vb = reinterpret_cast<const T*>(a.v) + b * a.v_sb + h * a.v_sh + 8 * c;
-    load_rows<T>(vb, a.v_sr, n_base, r0, N, col_live, raw);
-    float vmu[8];
-#pragma unroll
-    for (int e = 0; e < 8; ++e) vmu[e] = a.vmean ? a.vmean[(size_t)bh * HD + 8 * c + e] : 0.f;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const int t = r0 + 16 * i;                    // token within the tile; its 16-group is i
-      const long long n = n_base + t;
-      const bool live = n < N;
-      float x[8];
-      unpack8<T>(raw[i], x);
-      float amax = 0.f;
-#pragma unroll
-      for (int e = 0; e < 8; ++e) {
-        if (a.vmean) x[e] = (live && col_live) ? __fsub_rn(x[e], vmu[e]) : 0.f;
-        amax = fmaxf(amax, fabsf(x[e]));
-      }
-      amax = half_warp_max(amax);
-      const float sv = fmaxf(__fdiv_rn(amax, F8_MAX), SCALE_FLOOR);
-      const float rc = __frcp_rn(sv);
-      float y[8];
-#pragma unroll
-      for (int e = 0; e < 8; ++e) y[e] = fminf(div_by_scale(x[e], sv, rc), F8_MAX);
-      uint2 w;
-      w.x = e4m3x4(y[0], y[1], y[2], y[3]);
-      w.y = e4m3x4(y[4], y[5], y[6], y[7]);
-      // word column 2c (and 2c+1) of row t, XOR-swizzled by the row's 16-group so that the
-      // transposed read below is bank-conflict free
-      *reinterpret_cast<uint2*>(&vt[t * 32 + ((2 * c) ^ (i << 2))]) = w;
-      if (c == 0) {
-        a.sv[(size_t)bh * N_pad + n] = live ? sv : 0.0f;
-        if (live) svmax = fmaxf(svmax, sv);
-      }
-    }
-  }
-  __syncthreads();
-
-  // Transposed store: lane (tg = lane & 7, dqo = lane >> 3) of warp w takes the 4 channels
-  // 4*(4w + dqo) .. +3 for tokens 16*tg .. 16*tg + 15, i.e. four 16-byte stores; the eight tg
-  // lanes cover one 128-byte row of V8T.
-  {
-    const int tg = lane & 7, dq = 4 * warp + (lane >> 3);
-    uint32_t o[4][4];
-#pragma unroll
-    for (int g = 0; g < 4; ++g) {
-      uint32_t w0 = vt[(16 * tg + 4 * g + 0) * 32 + (dq ^ (tg << 2))];
-      uint32_t w1 = vt[(16 * tg + 4 * g + 1) * 32 + (dq ^ (tg << 2))];
-      uint32_t w2 = vt[(16 * tg + 4 * g + 2) * 32 + (dq ^ (tg << 2))];
-      uint32_t w3 = vt[(16 * tg + 4 * g + 3) * 32 + (dq ^ (tg << 2))];
-      const uint32_t t0 = __byte_perm(w0, w1, 0x5140), t1 = __byte_perm(w2, w3, 0x5140);
-      const uint32_t t2 = __byte_perm(w0, w1, 0x7362), t3 = __byte_perm(w2, w3, 0x7362);
-      o[0][g] = __byte_perm(t0, t1, 0x5410);
-      o[1][g] = __byte_perm(t0, t1, 0x7632);
-      o[2][g] = __byte_perm(t2, t3, 0x5410);
-      o[3][g] = __byte_perm(t2, t3, 0x7632);
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      uint8_t* dst = a.v8t + ((size_t)bh * HD + 4 * dq + e) * N_pad + n_base + 16 * tg;
-      *reinterpret_cast<uint4*>(dst) = make_uint4(o[e][0], o[e][1], o[e][2], o[e][3]);
-    }
-  }
-
-  // Per-head max of the V scale (all scales are >= 0, so the unsigned order of the bit patterns
-  // is the float order) and the last-CTA fold: S = max(max sv, 1), SVP = fl(fl(sv/S)*448).
-#pragma unroll
-  for (int off = 16; off > 0; off >>= 1) svmax = fmaxf(svmax, __shfl_xor_sync(0xffffffffu, svmax, off));
-  if (lane == 0) s_wmax[warp] = svmax;
-  __threadfence();                 // this thread's SV stores are visible before the arrival below
   __syncthreads();
   if (tid == 0) {
-    float m = s_wmax[0];
-#pragma unroll
-    for (int w = 1; w < 8; ++w) m = fmaxf(m, s_wmax[w]);
-    atomicMax(&a.svmax_bits[bh], __float_as_uint(m));
-    __threadfence();
-    s_last = (atomicAdd(&a.arrivals[bh], 1u) == (unsigned)(N_pad / TILE) - 1u);
+    for (int p = 0; p < QT_STAGES - 1; ++p) issue(p);
   }
-  __syncthreads();
-  if (s_last) {
-    __threadfence();
-    const float S = fmaxf(__uint_as_float(__ldcg(&a.svmax_bits[bh])), 1.0f);
-    if (tid == 0) a.s_fold[bh] = S;
-    for (long long n = tid; n < N_pad; n += 256) {
-      const float sv = __ldcg(&a.sv[(size_t)bh * N_pad + n]);
-      a.svp[(size_t)bh * N_pad + n] = __fmul_rn(__fdiv_rn(sv, S), F8_MAX);
+
+  for (uint32_t n = 0;; ++n) {
+    const int stage = (int)(n % QT_STAGES);
+    const uint32_t parity = (n / QT_STAGES) & 1u;
+    if (tid == 0) issue((int)((n + QT_STAGES - 1) % QT_STAGES));   // into the stage released by the previous item
+    // bounded wait for this item's tile
+    int ok = 1;
+    {
+      const uint32_t bar = bar0 + 8u * (uint32_t)stage;
+      if (!qt_try_wait(bar, parity)) {
+        const long long t0 = clock64();
+        uint32_t spins = 0;
+        while (!qt_try_wait(bar, parity)) {
+          if ((++spins & 1023u) == 0u && clock64() - t0 > QT_WAIT_CYCLES) { ok = 0; break; }
+        }
+      }
     }
+    if (!__syncthreads_and(ok)) {
+      if (tid == 0) { atomicOr(a.status, 1); if (a.status2) atomicOr(a.status2, 8); }
+      const long long t0 = clock64();
+      while (clock64() - t0 < 400000) { }     // give copies still in flight a moment to land
+      break;
+    }
+
+    const long long it = s_item[stage];
+    if (it < 0) break;                 // the list is exhausted (every thread reads the same value)
+    int which; long long bh, tile;
+    decode(it, which, bh, tile);
+    const long long n_base = tile * TILE;
+    const uint8_t* st = gbase + (size_t)stage * QT_STAGE_BYTES;
+
+    if (which == 0) {
+      // ---------------------------------- Q ----------------------------------
+      const long long N = a.Nq;
+      float mu[16];
+      if (a.qm != nullptr) {
+        const long long b = bh / a.Hq, h = bh - b * a.Hq, bh_kv = b * a.H + h / a.group;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) { mu[e] = a.mean[(size_t)bh_kv * HD + 8 * c + e]; mu[8 + e] = a.mean[(size_t)bh_kv * HD + 64 + 8 * c + e]; }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = r0 + 32 * i;
+        const long long nrow = n_base + t;
+        float x[16];
+        unpack8<T>(*reinterpret_cast<const uint4*>(st + t * 256 + 16 * c), x);
+        unpack8<T>(*reinterpret_cast<const uint4*>(st + t * 256 + 128 + 16 * c), x + 8);
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) amax = fmaxf(amax, fabsf(x[e]));
+        amax = fmaxf(quarter_warp_max(amax), SCALE_FLOOR);
+        const float qinv = __fdiv_rn(QMAX, amax);
+        float2 y[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) y[e] = make_float2(__fmul_rn(x[2 * e], qinv), __fmul_rn(x[2 * e + 1], qinv));
+        uint2 w0, w1;
+        if (INT8) {
+          w0.x = i8x4_magic2(y[0], y[1]); w0.y = i8x4_magic2(y[2], y[3]);
+          w1.x = i8x4_magic2(y[4], y[5]); w1.y = i8x4_magic2(y[6], y[7]);
+        } else {
+          w0.x = e4m3x4(y[0].x, y[0].y, y[1].x, y[1].y); w0.y = e4m3x4(y[2].x, y[2].y, y[3].x, y[3].y);
+          w1.x = e4m3x4(y[4].x, y[4].y, y[5].x, y[5].y); w1.y = e4m3x4(y[6].x, y[6].y, y[7].x, y[7].y);
+        }
+        if (nrow < N) {
+          uint8_t* dst = a.q8 + ((size_t)bh * N + nrow) * HD + 8 * c;
+          *reinterpret_cast<uint2*>(dst) = w0;
+          *reinterpret_cast<uint2*>(dst + 64) = w1;
+          if (c == 0) a.sq[(size_t)bh * N + nrow] = div_const<QDIV>(amax);
+        }
+        if (a.qm != nullptr) {                          // fixed-order fp32 dot product of the raw row
+          float d = 0.f;
+#pragma unroll
+          for (int e = 0; e < 16; ++e) d = __fmaf_rn(x[e], mu[e], d);
+          d += __shfl_xor_sync(0xffffffffu, d, 4);
+          d += __shfl_xor_sync(0xffffffffu, d, 2);
+          d += __shfl_xor_sync(0xffffffffu, d, 1);
+          if (c == 0 && nrow < N) a.qm[(size_t)bh * N + nrow] = d;
+        }
+      }
+    } else if (which == 1) {
+      // ---------------------------------- K ----------------------------------
+      const long long N = a.N, N_pad = a.N_pad;
+      float2 nmu[8];
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float* m0 = a.mean + (size_t)bh * HD + 8 * c + 2 * e;
+        nmu[e] = a.sub_mean ? make_float2(-m0[0], -m0[1]) : make_float2(0.f, 0.f);
+        nmu[4 + e] = a.sub_mean ? make_float2(-m0[64], -m0[65]) : make_float2(0.f, 0.f);
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = r0 + 32 * i;
+        const long long nrow = n_base + t;
+        const bool live = nrow < N;
+        float x[16];
+        unpack8<T>(*reinterpret_cast<const uint4*>(st + t * 256 + 16 * c), x);
+        unpack8<T>(*reinterpret_cast<const uint4*>(st + t * 256 + 128 + 16 * c), x + 8);
+        float2 xs[8];
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          xs[e] = __fadd2_rn(make_float2(x[2 * e], x[2 * e + 1]), nmu[e]);
+          amax = fmaxf(amax, fmaxf(fabsf(xs[e].x), fabsf(xs[e].y)));
+        }
+        amax = quarter_warp_max(live ? amax : 0.f);
+        const float sk = fmaxf(div_const<QDIV>(amax), SCALE_FLOOR);
+        const float rc = __frcp_rn(sk);
+        uint2 w0, w1;
+        if (INT8) {
+          // the sign of a zero quotient does not reach an int8 code, so the packed form is enough
+          const float2 rc2 = make_float2(rc, rc), ns2 = make_float2(-sk, -sk);
+          float2 y[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            const float2 q0 = __fmul2_rn(xs[e], rc2);
+            const float2 r = __ffma2_rn(q0, ns2, xs[e]);
+            y[e] = __ffma2_rn(r, rc2, q0);
+          }
+          w0.x = i8x4_magic2(y[0], y[1]); w0.y = i8x4_magic2(y[2], y[3]);
+          w1.x = i8x4_magic2(y[4], y[5]); w1.y = i8x4_magic2(y[6], y[7]);
+        } else {
+          float y[16];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { y[2 * e] = div_by_scale(xs[e].x, sk, rc); y[2 * e + 1] = div_by_scale(xs[e].y, sk, rc); }
+          w0.x = e4m3x4(y[0], y[1], y[2], y[3]); w0.y = e4m3x4(y[4], y[5], y[6], y[7]);
+          w1.x = e4m3x4(y[8], y[9], y[10], y[11]); w1.y = e4m3x4(y[12], y[13], y[14], y[15]);
+        }
+        if (!live) { w0 = make_uint2(0u, 0u); w1 = w0; }
+        uint8_t* dst = a.k8 + ((size_t)bh * N_pad + nrow) * HD + 8 * c;
+        *reinterpret_cast<uint2*>(dst) = w0;
+        *reinterpret_cast<uint2*>(dst + 64) = w1;
+        if (c == 0) a.sk[(size_t)bh * N_pad + nrow] = live ? sk : 1.0f;
+      }
+    } else {
+      // ---------------------------------- V ----------------------------------
+      const long long N = a.N, N_pad = a.N_pad;
+      float vmu[16];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        vmu[e] = a.vmean ? a.vmean[(size_t)bh * HD + 8 * c + e] : 0.f;
+        vmu[8 + e] = a.vmean ? a.vmean[(size_t)bh * HD + 64 + 8 * c + e] : 0.f;
+      }
+      float svmax = 0.f;
+      uint2 w0[4], w1[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = r0 + 32 * i;
+        const long long nrow = n_base + t;
+        const bool live = nrow < N;
+        float x[16];
+        unpack8<T>(*reinterpret_cast<const uint4*>(st + t * 256 + 16 * c), x);
+        unpack8<T>(*reinterpret_cast<const uint4*>(st + t * 256 + 128 + 16 * c), x + 8);
+        float amax = 0.f;
+#pragma unroll
+        for (int e = 0; e < 16; ++e) {
+          if (a.vmean) x[e] = live ? __fsub_rn(x[e], vmu[e]) : 0.f;
+          amax = fmaxf(amax, fabsf(x[e]));
+        }
+        amax = quarter_warp_max(amax);
+        const float sv = fmaxf(div_const<448>(amax), SCALE_FLOOR);
+        const float rc = __frcp_rn(sv);
+        float y[16];
+#pragma unroll
+        for (int e = 0; e < 16; ++e) y[e] = div_by_scale(x[e], sv, rc);
+        w0[i].x = e4m3x4(y[0], y[1], y[2], y[3]); w0[i].y = e4m3x4(y[4], y[5], y[6], y[7]);
+        w1[i].x = e4m3x4(y[8], y[9], y[10], y[11]); w1[i].y = e4m3x4(y[12], y[13], y[14], y[15]);
+        if (c == 0) {
+          a.sv[(size_t)bh * N_pad + nrow] = live ? sv : 0.0f;
+          if (live) svmax = fmaxf(svmax, sv);
+        }
+      }
+      __syncthreads();                 // every thread has read its rows: the stage becomes the code tile
+      uint32_t* vt = reinterpret_cast<uint32_t*>(gbase + (size_t)stage * QT_STAGE_BYTES);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int t = r0 + 32 * i;
+        const int key = (((t >> 4) & 7) << 2) ^ ((t & 1) << 4);
+        *reinterpret_cast<uint2*>(&vt[t * 32 + ((2 * c) ^ key)]) = w0[i];
+        *reinterpret_cast<uint2*>(&vt[t * 32 + ((16 + 2 * c) ^ key)]) = w1[i];
+      }
+      __syncthreads();
+      {
+        const int tg = lane & 7, dq = 4 * warp + (lane >> 3);
+        uint32_t o[4][4];
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          const int tk = 16 * tg + 4 * g;
+          const uint32_t w0_ = vt[(tk + 0) * 32 + (dq ^ (tg << 2))];
+          const uint32_t w1_ = vt[(tk + 1) * 32 + (dq ^ (tg << 2) ^ 16)];
+          const uint32_t w2_ = vt[(tk + 2) * 32 + (dq ^ (tg << 2))];
+          const uint32_t w3_ = vt[(tk + 3) * 32 + (dq ^ (tg << 2) ^ 16)];
+          const uint32_t t0 = __byte_perm(w0_, w1_, 0x5140), t1 = __byte_perm(w2_, w3_, 0x5140);
+          const uint32_t t2 = __byte_perm(w0_, w1_, 0x7362), t3 = __byte_perm(w2_, w3_, 0x7362);
+          o[0][g] = __byte_perm(t0, t1, 0x5410);
+          o[1][g] = __byte_perm(t0, t1, 0x7632);
+          o[2][g] = __byte_perm(t2, t3, 0x5410);
+          o[3][g] = __byte_perm(t2, t3, 0x7632);
+        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          uint8_t* dst = a.v8t + ((size_t)bh * HD + 4 * dq + e) * N_pad + n_base + 16 * tg;
+          *reinterpret_cast<uint4*>(dst) = make_uint4(o[e][0], o[e][1], o[e][2], o[e][3]);
+        }
+      }
+      // per-head max of the V scale (all scales are >= 0, so the unsigned order of the bit patterns
+      // is the float order); S and SVP are folded by fold_sv_kernel once every tile is in
+#pragma unroll
+      for (int off = 16; off > 0; off >>= 1) svmax = fmaxf(svmax, __shfl_xor_sync(0xffffffffu, svmax, off));
+      if (lane == 0 && svmax > 0.f) atomicMax(&a.svmax_bits[bh], __float_as_uint(svmax));
+    }
+    __syncthreads();                   // the stage may be refilled
   }
 }
 
 // ------------------------------------------------------------------------------------------------
 // Host launcher.
 // ------------------------------------------------------------------------------------------------
+// S = max(max sv, 1) and SVP = fl(fl(sv / S) * 448) for every key of every head (the reference's
+// fold_v_scale followed by the attention kernel's staging).  grid (ceil(N_pad / 1024), B*H).
+__global__ void __launch_bounds__(256)
+fold_sv_kernel(const float* __restrict__ sv, const unsigned* __restrict__ svmax_bits, float* __restrict__ svp,
+               float* __restrict__ s_fold, long long N_pad) {
+  const int bh = blockIdx.y;
+  const float S = fmaxf(__uint_as_float(svmax_bits[bh]), 1.0f);
+  if (blockIdx.x == 0 && threadIdx.x == 0) s_fold[bh] = S;
+  const long long n = ((long long)blockIdx.x * 256 + threadIdx.x) * 4;
+  if (n < N_pad) {                                    // N_pad is a multiple of 128: whole float4s
+    const float4 v = *reinterpret_cast<const float4*>(sv + (size_t)bh * N_pad + n);
+    float4 o;
+    o.x = __fmul_rn(__fdiv_rn(v.x, S), F8_MAX); o.y = __fmul_rn(__fdiv_rn(v.y, S), F8_MAX);
+    o.z = __fmul_rn(__fdiv_rn(v.z, S), F8_MAX); o.w = __fmul_rn(__fdiv_rn(v.w, S), F8_MAX);
+    *reinterpret_cast<float4*>(svp + (size_t)bh * N_pad + n) = o;
+  }
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (!fn) {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  }
+  return fn;
+}
+// 4-D map over a logical (B, H, N, D) view of 2-byte elements with (batch, head, row) element
+// strides: box 128 columns x 128 rows, no swizzle, out-of-range elements read as zero.
+static bool make_map4(CUtensorMap* m, const void* ptr, CUtensorMapDataType dt, int64_t D, int64_t N, int64_t H,
+                      int64_t B, const int64_t strides_bhr[3]) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)N, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)strides_bhr[2] * 2, (cuuint64_t)strides_bhr[1] * 2, (cuuint64_t)strides_bhr[0] * 2};
+  cuuint32_t box[4] = {128, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(m, dt, 4, const_cast<void*>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 template <typename T>
 static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   const int64_t bh = p.B * p.H;
@@ -377,22 +510,49 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     if (e != cudaSuccess) return e;
   }
   QuantArgs a;
-  a.q = p.q; a.k = p.k; a.v = p.v;
   a.q8 = reinterpret_cast<uint8_t*>(p.q8); a.k8 = reinterpret_cast<uint8_t*>(p.k8);
   a.v8t = reinterpret_cast<uint8_t*>(p.v8t);
-  a.sq = p.sq; a.sk = p.sk; a.sv = p.sv; a.svp = p.svp; a.s_fold = p.s_fold; a.mean = p.mean; a.vmean = p.vmean;
-  a.arrivals = words + bh; a.svmax_bits = words + 2 * bh;
+  a.sq = p.sq; a.sk = p.sk; a.sv = p.sv; a.mean = p.mean; a.vmean = p.vmean;
+  a.svmax_bits = words + 2 * bh;
   a.N = p.N; a.N_pad = p.N_pad; a.H = p.H;
   a.Nq = p.Nq; a.Hq = p.Hq; a.group = p.Hq / p.H; a.BHq = p.B * p.Hq; a.BHkv = bh; a.qm = p.qm;
-  a.q_sb = p.q_strides[0]; a.q_sh = p.q_strides[1]; a.q_sr = p.q_strides[2];
-  a.k_sb = p.k_strides[0]; a.k_sh = p.k_strides[1]; a.k_sr = p.k_strides[2];
-  a.v_sb = p.v_strides[0]; a.v_sh = p.v_strides[1]; a.v_sr = p.v_strides[2];
   a.sub_mean = p.smooth_k ? 1 : 0;
-  a.D = (int)p.D;
   const int64_t tq = (p.Nq + TILE - 1) / TILE, tk = p.N_pad / TILE;
-  dim3 grid((unsigned)(tq > tk ? tq : tk), (unsigned)(a.BHq > bh ? a.BHq : bh), 3);
-  if (p.qk_mode == 0) quant_qkv_kernel<T, true><<<grid, 256, 0, st>>>(a);
-  else quant_qkv_kernel<T, false><<<grid, 256, 0, st>>>(a);
+  a.status = reinterpret_cast<int32_t*>(words + CtrlHeader::status_word(bh));
+  a.status2 = p.status;
+  a.next_item = reinterpret_cast<unsigned long long*>(words + CtrlHeader::status_word(bh) + 2);
+  CUtensorMap mq, mk, mv;
+  const CUtensorMapDataType dt = (sizeof(T) == 2 && std::is_same<T, __half>::value) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                                                      : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  if (!make_map4(&mq, p.q, dt, p.D, p.Nq, p.Hq, p.B, p.q_strides) ||
+      !make_map4(&mk, p.k, dt, p.D, p.N, p.H, p.B, p.k_strides) ||
+      !make_map4(&mv, p.v, dt, p.D, p.N, p.H, p.B, p.v_strides))
+    return cudaErrorInvalidValue;
+  // SM count and the opt-in to 64 KB of dynamic shared memory: looked up once per device
+  static int sm_count[64] = {0};
+  static bool opted_in[64][2] = {{false}};
+  int dev = 0;
+  e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (sm_count[dev] == 0) {
+    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+  }
+  const long long total = 2 * (long long)bh * tk + (long long)a.BHq * tq;
+  long long ctas = (long long)sm_count[dev] * QT_MINBLOCKS;
+  if (ctas > total) ctas = total;
+  auto kern = (p.qk_mode == 0) ? quant_qkv_kernel<T, true> : quant_qkv_kernel<T, false>;
+  if (!opted_in[dev][p.qk_mode == 0]) {
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QT_SMEM_BYTES);
+    if (e != cudaSuccess) return e;
+    opted_in[dev][p.qk_mode == 0] = true;
+  }
+  kern<<<(unsigned)ctas, 256, QT_SMEM_BYTES, st>>>(mq, mk, mv, a);
+  e = cudaGetLastError();
+  if (e != cudaSuccess) return e;
+  dim3 fgrid((unsigned)((p.N_pad + 1023) / 1024), (unsigned)bh);
+  fold_sv_kernel<<<fgrid, 256, 0, st>>>(p.sv, words + 2 * bh, p.svp, p.s_fold, p.N_pad);
   return cudaGetLastError();
 }
 
