@@ -32,7 +32,7 @@ struct CtrlHeader {
 
 // How many CTAs share one head's sequence in the mean kernel.
 inline int kmean_splits(int64_t bh, int64_t n) {
-  int64_t want = (6 * 148 + bh - 1) / bh;          // about six CTAs per SM in total
+  int64_t want = (4 * 148) / bh;                   // one full wave: four resident CTAs on each of 148 SMs
   int64_t cap = (n + 255) / 256;                   // at least 256 tokens per CTA
   if (want > cap) want = cap;
   if (want > 64) want = 64;

@@ -74,7 +74,7 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
 
 def test_oversized_shape_is_refused_before_any_launch():
     lib = _native.load()
-    b, h, n = 8, 64, 64 * 1024           # 512 heads: the mean's partial sums alone exceed 1 MiB
+    b, h, n = 32, 64, 64 * 1024          # 2048 heads: the mean's partial sums alone exceed 1 MiB
     assert lib.sage_prologue_ctrl_bytes(b, h, n) > lib.sage_prologue_static_ctrl_capacity()
     dummy = torch.zeros(64, dtype=torch.uint8, device="cuda")
     p = ctypes.c_void_p(int(dummy.data_ptr()))
