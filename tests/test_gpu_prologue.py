@@ -100,3 +100,29 @@ def test_full_size_properties():
     assert pq["q8"].abs().amax(dim=2).min().item() == 127
     ref = R.prologue(q, k, v, pad_multiple=128)                       # torch ops on the device
     _check_against(pq, ref, n, True)
+
+
+@pytest.mark.parametrize("b,h,n", [(16, 40, 70), (3, 200, 129), (1, 1, 5000)])
+def test_many_units_and_the_work_counter(b, h, n):
+    """More (tensor, head, tile) items than persistent CTAs, and fewer: every item is quantised
+    exactly once whatever order the CTAs draw them in, and the status word stays clear."""
+    q, k, v = R.make_inputs(b, h, n, 128, torch.float16, seed=b + h + n, k_bias_std=0.3)
+    ref = R.prologue(q, k, v, smooth_k=True, pad_multiple=128)
+    pq = be.quant_qkv(q.cuda(), k.cuda(), v.cuda(), smooth_k=True)
+    again = be.quant_qkv(q.cuda(), k.cuda(), v.cuda(), smooth_k=True, reuse=pq)     # same buffers, second run
+    _check_against(again, ref, n, True)
+    words = pq["ctrl"].view(torch.int32)
+    assert int(words[4 * b * h].item()) == 0                                          # the quantiser's status word
+    items = 2 * b * h * ((n + 127) // 128) + b * h * ((n + 127) // 128)
+    counter = int(pq["ctrl"][4 * (4 * b * h + 2): 4 * (4 * b * h + 2) + 8].view(torch.int64).item())
+    assert counter >= items                                                            # every item was drawn
+
+
+def test_prologue_is_deterministic_across_runs():
+    q, k, v = R.make_inputs(2, 6, 1500, 128, torch.bfloat16, seed=77, k_bias_std=0.5, device="cuda")
+    a = be.quant_qkv(q, k, v)
+    b = be.quant_qkv(q, k, v)
+    for key in ("q8", "k8", "v8t"):
+        assert bytes_equal(a[key], b[key].cpu()), key
+    for key in ("sq", "sk", "sv", "svp", "S", "mean"):
+        assert torch.equal(a[key], b[key]), key
