@@ -319,7 +319,7 @@ def main() -> int:
     o2 = torch.empty_like(q)
     st = torch.zeros(1, dtype=torch.int32, device=dev)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
-    pro_ms, att_ms = [], []
+    att_ms = []
     for i in range(args.warmup + args.steps):
         ev[0].record(stream)
         pq = be.quant_qkv(q, k, v, reuse=pq)
@@ -328,10 +328,17 @@ def main() -> int:
         ev[2].record(stream)
         torch.cuda.synchronize(dev)
         if i >= args.warmup:
-            pro_ms.append(ev[0].elapsed_time(ev[1]))
             att_ms.append(ev[1].elapsed_time(ev[2]))
     att = statistics.mean(att_ms)
-    pro = statistics.mean(pro_ms)
+    # The prologue lasts about half a millisecond: timed call by call from an idle GPU, the host's
+    # launch latency before the first kernel would be counted as kernel time.  So it is timed as a
+    # back-to-back batch (the GPU is still busy with call i when call i+1 is enqueued).
+    ev[0].record(stream)
+    for _ in range(args.steps):
+        pq = be.quant_qkv(q, k, v, reuse=pq)
+    ev[1].record(stream)
+    torch.cuda.synchronize(dev)
+    pro = ev[0].elapsed_time(ev[1]) / args.steps
     pk = peaks()
     peak8 = 2.0 * pk["bf16_tflops_sustained"]
     achieved = flops(causal) / (att * 1e-3) / 1e12
@@ -341,7 +348,7 @@ def main() -> int:
                                "vs 2 x burst %.0f: %.3f; vs nominal 4500: %.3f"
                                % (pk["source"], 2 * pk["bf16_tflops"], achieved / (2 * pk["bf16_tflops"]), achieved / 4500.0))
     pro_gbs = prologue_bytes() / (pro * 1e-3) / 1e9
-    prologue = dict(bound="hbm", kernel="kmean_kernel + quant_qkv_kernel + fold_sv_kernel (+ memset)", achieved=pro_gbs, peak=pk["hbm_gbs"],
+    prologue = dict(bound="hbm", kernel="kmean_kernel + quant_qkv_kernel (+ memset)", achieved=pro_gbs, peak=pk["hbm_gbs"],
                     unit="GB/s", frac=pro_gbs / pk["hbm_gbs"], ms=pro, algorithmic_bytes=prologue_bytes())
 
     # ---- end to end from pinned host buffers through the public API ----
@@ -422,7 +429,7 @@ def main() -> int:
         line = dict(metric=METRIC, value=value, unit="TFLOP/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
                     ms_per_step=ms_step, higher_is_better=True, scaling="weak", vs_baseline=None,
                     dtype="int8+fp8", data="synthetic", config=workload_config(causal, world),
-                    roofline=roofline, prologue=prologue, e2e=e2e, gpu_launches=4 * args.steps,
+                    roofline=roofline, prologue=prologue, e2e=e2e, gpu_launches=3 * args.steps,
                     clocks=clk.summary(), kernel_status=status)
         if others is not None:
             line["other_arms"] = others

@@ -72,7 +72,7 @@ size_t sage_prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
  *             ran out (the outputs are then undefined); sage_attention reports the same event as
  *             bit 8 of its status word
  *   N_pad     must equal sage_pad_len(N)
- * Three kernel launches (mean, quantise, fold of S and svp) and one small memset. */
+ * Two kernel launches (mean, quantise) and one small memset. */
 int sage_prologue(const void* q, const void* k, const void* v,
                   void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
                   float* s_fold, float* mean, void* ctrl,

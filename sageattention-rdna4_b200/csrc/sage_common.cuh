@@ -18,7 +18,7 @@ constexpr float LOG2E_F = 1.4426950408889634f;
 
 // Control block of the prologue (device memory, zeroed by a memset at the start of every call).
 struct CtrlHeader {
-  // per head: [0] arrivals of the K mean kernel, [1] unused, [2] max V scale bits, [3] arrivals
+  // per head: [0] arrivals of the K mean kernel, [1] V tiles quantised so far, [2] max V scale bits, [3] arrivals
   // of the V mean kernel (smooth_v), laid out as four arrays of BH words; then one status word
   // (non-zero when a wait inside the quantiser ran out), one pad word and the quantiser's 64-bit
   // work counter; the fp64 partial sums (shared by the two mean launches, which run one after the

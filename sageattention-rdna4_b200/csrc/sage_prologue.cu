@@ -1,7 +1,7 @@
 // Quantisation prologue for B200: sequence mean of K (smooth_k; of V too with smooth_v), then one
 // persistent, TMA-fed pass over the 128-token tiles of K, V and Q that writes the int8 / e4m3
-// codes, the per-token scales and V transposed, then a small kernel that folds the per-head S and
-// its staged factor.
+// codes, the per-token scales and V transposed, and closes with the fold of the per-head S and its
+// staged factor.
 //
 // Arithmetic contract (reference: kernels/hip/h34_prologue.hip:116-211,259-282;
 // kernels/hip/sk1_t6i.hip:104-117; kernels/hip/sk1_t4a1sb.hip:89-100;
@@ -91,10 +91,11 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
 // ------------------------------------------------------------------------------------------------
 struct QuantArgs {
   uint8_t *q8, *k8, *v8t;
-  float *sq, *sk, *sv;
+  float *sq, *sk, *sv, *svp, *s_fold;
   const float* mean;
   const float* vmean;             // optional: sequence mean of V, subtracted before quantising (smooth_v)
   unsigned* svmax_bits;           // per K/V head: running maximum of the V scales, as float bits
+  unsigned* arrivals;             // per K/V head: V tiles whose scales are published
   long long N, N_pad, H;          // keys: length, padded length, K/V heads per batch element
   long long Nq, Hq, group;        // queries: length, heads per batch element, Hq / H (1 without GQA)
   long long BHq, BHkv;            // B*Hq, B*H
@@ -123,6 +124,7 @@ __device__ __forceinline__ float div_by_scale(float x, float s, float rc) {
 // ------------------------------------------------------------------------------------------------
 constexpr int QT_STAGES = 2;        // shared-memory ring: one tile being quantised, one in flight
 constexpr int QT_MINBLOCKS = 3;     // CTAs per SM (3 x 64 KB of shared memory, 80 registers per thread)
+constexpr int FOLD_KEYS = 4096;     // keys per fold item
 constexpr uint32_t QT_STAGE_BYTES = TILE * HD * 2;
 constexpr uint32_t QT_SMEM_BYTES = QT_STAGES * QT_STAGE_BYTES + 128 /* alignment slack */ + 64 /* barriers */;
 constexpr long long QT_WAIT_CYCLES = 4000000000LL;
@@ -173,14 +175,17 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
   const long long tiles_q = (a.Nq + TILE - 1) / TILE, tiles_k = a.N_pad / TILE;
   const long long items_k = a.BHkv * tiles_k, items_q = a.BHq * tiles_q;
-  const long long total = 2 * items_k + items_q;
+  const long long fold_per_head = (a.N_pad + FOLD_KEYS - 1) / FOLD_KEYS;
+  const long long items_f = a.BHkv * fold_per_head;
+  const long long total = 2 * items_k + items_q + items_f;
 
   // item -> (tensor, head, tile): K first with the last heads first (their rows are still in L2
   // after the mean pass), then V (so that the per-head folds overlap the Q items), then Q
   auto decode = [&](long long it, int& which, long long& bh, long long& tile) {
     if (it < items_k) { which = 1; bh = a.BHkv - 1 - it / tiles_k; tile = it % tiles_k; }
     else if (it < 2 * items_k) { const long long j = it - items_k; which = 2; bh = a.BHkv - 1 - j / tiles_k; tile = j % tiles_k; }
-    else { const long long j = it - 2 * items_k; which = 0; bh = a.BHq - 1 - j / tiles_q; tile = j % tiles_q; }
+    else if (it < 2 * items_k + items_q) { const long long j = it - 2 * items_k; which = 0; bh = a.BHq - 1 - j / tiles_q; tile = j % tiles_q; }
+    else { const long long j = it - 2 * items_k - items_q; which = 3; bh = a.BHkv - 1 - j / fold_per_head; tile = j % fold_per_head; }
   };
   // Items are handed out through one global counter: a CTA that is held up (by a head's fold, say)
   // simply takes fewer of them.  Thread 0 draws the item for a stage, publishes it in s_item and
@@ -196,6 +201,10 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     s_item[stage] = it;
     int which; long long bh, tile;
     decode(it, which, bh, tile);
+    if (which == 3) {                  // fold items read no tile
+      asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_) : "memory");
+      return;
+    }
     const long long heads = (which == 0) ? a.Hq : a.H;
     const int b = (int)(bh / heads), h = (int)(bh - (long long)b * heads);
     const CUtensorMap* map = (which == 0) ? &tm_q : (which == 1 ? &tm_k : &tm_v);
@@ -348,7 +357,7 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         *reinterpret_cast<uint2*>(dst + 64) = w1;
         if (c == 0) a.sk[(size_t)bh * N_pad + nrow] = live ? sk : 1.0f;
       }
-    } else {
+    } else if (which == 2) {
       // ---------------------------------- V ----------------------------------
       const long long N = a.N, N_pad = a.N_pad;
       float vmu[16];
@@ -420,36 +429,57 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
       }
       // per-head max of the V scale (all scales are >= 0, so the unsigned order of the bit patterns
-      // is the float order); S and SVP are folded by fold_sv_kernel once every tile is in
+      // is the float order); S and SVP are folded by the closing items of the list
 #pragma unroll
       for (int off = 16; off > 0; off >>= 1) svmax = fmaxf(svmax, __shfl_xor_sync(0xffffffffu, svmax, off));
       if (lane == 0 && svmax > 0.f) atomicMax(&a.svmax_bits[bh], __float_as_uint(svmax));
+    } else if (which == 3) {
+      // ------------------------- fold of one head's V scales -------------------------
+      // S = max(max sv, 1), SVP = fl(fl(sv / S) * 448) for FOLD_KEYS keys (the reference's
+      // fold_v_scale and the attention kernel's staging).  These items close the list, long after
+      // the head's V tiles were drawn; thread 0 still waits, bounded, for their arrivals.
+      int done = 1;
+      if (tid == 0) {
+        const unsigned want = (unsigned)tiles_k;
+        const volatile unsigned* arr = a.arrivals + bh;
+        if (*arr != want) {
+          const long long t0 = clock64();
+          while (*arr != want) {
+            if (clock64() - t0 > QT_WAIT_CYCLES) { done = 0; break; }
+          }
+        }
+        __threadfence();               // acquire: the V scales of every arrived tile are visible
+      }
+      if (!__syncthreads_and(done)) {
+        if (tid == 0) { atomicOr(a.status, 2); if (a.status2) atomicOr(a.status2, 8); }
+        break;
+      }
+      const long long N_pad = a.N_pad;
+      const float S = fmaxf(__uint_as_float(__ldcg(&a.svmax_bits[bh])), 1.0f);
+      if (tile == 0 && tid == 0) a.s_fold[bh] = S;
+#pragma unroll
+      for (int i = 0; i < FOLD_KEYS / 1024; ++i) {
+        const long long nn = tile * FOLD_KEYS + (long long)i * 1024 + 4 * tid;
+        if (nn < N_pad) {              // N_pad is a multiple of 128: whole float4s
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(a.sv + (size_t)bh * N_pad + nn));
+          float4 o;
+          o.x = __fmul_rn(__fdiv_rn(v.x, S), F8_MAX); o.y = __fmul_rn(__fdiv_rn(v.y, S), F8_MAX);
+          o.z = __fmul_rn(__fdiv_rn(v.z, S), F8_MAX); o.w = __fmul_rn(__fdiv_rn(v.w, S), F8_MAX);
+          *reinterpret_cast<float4*>(a.svp + (size_t)bh * N_pad + nn) = o;
+        }
+      }
     }
     __syncthreads();                   // the stage may be refilled
+    if (which == 2 && tid == 0) {      // this tile's V scales and maximum are published: one release per CTA
+      __threadfence();
+      atomicAdd(a.arrivals + bh, 1u);
+    }
   }
 }
 
 // ------------------------------------------------------------------------------------------------
 // Host launcher.
 // ------------------------------------------------------------------------------------------------
-// S = max(max sv, 1) and SVP = fl(fl(sv / S) * 448) for every key of every head (the reference's
-// fold_v_scale followed by the attention kernel's staging).  grid (ceil(N_pad / 1024), B*H).
-__global__ void __launch_bounds__(256)
-fold_sv_kernel(const float* __restrict__ sv, const unsigned* __restrict__ svmax_bits, float* __restrict__ svp,
-               float* __restrict__ s_fold, long long N_pad) {
-  const int bh = blockIdx.y;
-  const float S = fmaxf(__uint_as_float(svmax_bits[bh]), 1.0f);
-  if (blockIdx.x == 0 && threadIdx.x == 0) s_fold[bh] = S;
-  const long long n = ((long long)blockIdx.x * 256 + threadIdx.x) * 4;
-  if (n < N_pad) {                                    // N_pad is a multiple of 128: whole float4s
-    const float4 v = *reinterpret_cast<const float4*>(sv + (size_t)bh * N_pad + n);
-    float4 o;
-    o.x = __fmul_rn(__fdiv_rn(v.x, S), F8_MAX); o.y = __fmul_rn(__fdiv_rn(v.y, S), F8_MAX);
-    o.z = __fmul_rn(__fdiv_rn(v.z, S), F8_MAX); o.w = __fmul_rn(__fdiv_rn(v.w, S), F8_MAX);
-    *reinterpret_cast<float4*>(svp + (size_t)bh * N_pad + n) = o;
-  }
-}
-
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
                                   CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
@@ -512,8 +542,8 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   QuantArgs a;
   a.q8 = reinterpret_cast<uint8_t*>(p.q8); a.k8 = reinterpret_cast<uint8_t*>(p.k8);
   a.v8t = reinterpret_cast<uint8_t*>(p.v8t);
-  a.sq = p.sq; a.sk = p.sk; a.sv = p.sv; a.mean = p.mean; a.vmean = p.vmean;
-  a.svmax_bits = words + 2 * bh;
+  a.sq = p.sq; a.sk = p.sk; a.sv = p.sv; a.svp = p.svp; a.s_fold = p.s_fold; a.mean = p.mean; a.vmean = p.vmean;
+  a.svmax_bits = words + 2 * bh; a.arrivals = words + bh;
   a.N = p.N; a.N_pad = p.N_pad; a.H = p.H;
   a.Nq = p.Nq; a.Hq = p.Hq; a.group = p.Hq / p.H; a.BHq = p.B * p.Hq; a.BHkv = bh; a.qm = p.qm;
   a.sub_mean = p.smooth_k ? 1 : 0;
@@ -549,10 +579,6 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     opted_in[dev][p.qk_mode == 0] = true;
   }
   kern<<<(unsigned)ctas, 256, QT_SMEM_BYTES, st>>>(mq, mk, mv, a);
-  e = cudaGetLastError();
-  if (e != cudaSuccess) return e;
-  dim3 fgrid((unsigned)((p.N_pad + 1023) / 1024), (unsigned)bh);
-  fold_sv_kernel<<<fgrid, 256, 0, st>>>(p.sv, words + 2 * bh, p.svp, p.s_fold, p.N_pad);
   return cudaGetLastError();
 }
 
