@@ -210,22 +210,9 @@ __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
 // Shared-memory accesses through 32-bit shared-window addresses (half the registers of a pointer).
-#ifndef SAGE_SCALE_LD
-#define SAGE_SCALE_LD 128
-#endif
 __device__ __forceinline__ float4 lds128(uint32_t addr) {
   float4 v;
-#if SAGE_SCALE_LD == 128
   asm volatile("ld.shared.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr));
-#elif SAGE_SCALE_LD == 64
-  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "r"(addr));
-  asm volatile("ld.shared.v2.f32 {%0, %1}, [%2+8];" : "=f"(v.z), "=f"(v.w) : "r"(addr));
-#else
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v.x) : "r"(addr));
-  asm volatile("ld.shared.f32 %0, [%1+4];" : "=f"(v.y) : "r"(addr));
-  asm volatile("ld.shared.f32 %0, [%1+8];" : "=f"(v.z) : "r"(addr));
-  asm volatile("ld.shared.f32 %0, [%1+12];" : "=f"(v.w) : "r"(addr));
-#endif
   return v;
 }
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
@@ -291,10 +278,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 // The kernel.  grid (ceil(N/128), B*H), block 384, two CTAs per SM.
 // ------------------------------------------------------------------------------------------------
 template <bool INT8, bool CAUSAL, typename OutT>
-#ifndef SAGE_ATT_MINBLOCKS
-#define SAGE_ATT_MINBLOCKS 2
-#endif
-__global__ void __launch_bounds__(ATT_THREADS, SAGE_ATT_MINBLOCKS)
+__global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
   extern __shared__ uint8_t smem_raw[];

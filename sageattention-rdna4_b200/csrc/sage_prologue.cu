@@ -188,10 +188,11 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     else { const long long j = it - 2 * items_k - items_q; which = 3; bh = a.BHkv - 1 - j / fold_per_head; tile = j % fold_per_head; }
   };
   // Items are handed out through one global counter: a CTA that is held up (by a head's fold, say)
-  // simply takes fewer of them.  Thread 0 draws the item for a stage, publishes it in s_item and
-  // starts its load; past the end it publishes -1 and completes the stage's barrier by hand.
-  auto issue = [&](int stage) {
-    const long long it = (long long)atomicAdd(a.next_item, 1ULL);
+  // simply takes fewer of them.  Thread 0 publishes the item of a stage in s_item and starts its
+  // load; past the end it publishes -1 and completes the stage's barrier by hand.  The counter is
+  // drawn one item ahead, so the atomic's round trip is off the critical path.
+  auto draw = [&]() { return (long long)atomicAdd(a.next_item, 1ULL); };
+  auto issue = [&](int stage, long long it) {
     const uint32_t bar_ = bar0 + 8u * (uint32_t)stage;
     if (it >= total) {
       s_item[stage] = -1;
@@ -221,14 +222,19 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   __syncthreads();
+  long long drawn = 0;
   if (tid == 0) {
-    for (int p = 0; p < QT_STAGES - 1; ++p) issue(p);
+    for (int p = 0; p < QT_STAGES - 1; ++p) issue(p, draw());
+    drawn = draw();
   }
 
   for (uint32_t n = 0;; ++n) {
     const int stage = (int)(n % QT_STAGES);
     const uint32_t parity = (n / QT_STAGES) & 1u;
-    if (tid == 0) issue((int)((n + QT_STAGES - 1) % QT_STAGES));   // into the stage released by the previous item
+    if (tid == 0) {                    // into the stage released by the previous item
+      issue((int)((n + QT_STAGES - 1) % QT_STAGES), drawn);
+      drawn = draw();                  // consumed one iteration later
+    }
     // bounded wait for this item's tile
     int ok = 1;
     {
