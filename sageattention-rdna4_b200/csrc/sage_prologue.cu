@@ -210,6 +210,9 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int b = (int)(bh / heads), h = (int)(bh - (long long)b * heads);
     const CUtensorMap* map = (which == 0) ? &tm_q : (which == 1 ? &tm_k : &tm_v);
     const uint32_t bar = bar0 + 8u * (uint32_t)stage, dst = base + (uint32_t)stage * QT_STAGE_BYTES;
+    // the stage was last touched by ordinary loads and stores (V tiles are staged back into it);
+    // order them before the copy engine's writes
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(QT_STAGE_BYTES) : "memory");
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"

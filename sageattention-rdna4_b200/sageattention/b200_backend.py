@@ -29,7 +29,6 @@ STRIDED_REFUSALS = ("rank", "stride_last", "stride_nonpos", "stride_align", "ptr
                     "stride_overlap", "stride_int32")
 
 _counters = {"calls": 0, "refusals": 0}
-_counters_lock = threading.Lock()
 
 
 def pad_len(n: int) -> int:
@@ -229,6 +228,58 @@ def clear_workspaces():
         _ws_cache.clear()
 
 
+# Calls repeat with the same shapes and strides (a diffusion transformer issues the same attention
+# call thousands of times), and for sequences of a few hundred tokens the GPU work is shorter than
+# a careless host path.  A call signature that has passed `envelope_reason` once is remembered with
+# everything derived from it (logical dims, stride triples for the C call), so the hot path is a
+# handful of attribute reads, one dictionary lookup and the C call.
+_sig_cache: Dict[Tuple, Tuple] = {}
+_SIG_CACHE_ENTRIES = 256
+
+
+def _logical_strides(t: torch.Tensor, nhd: bool):
+    st = t.stride()
+    return (st[0], st[2], st[1]) if nhd else (st[0], st[1], st[2])
+
+
+def _validated(q, k, v, tensor_layout):
+    """(b, hq, hkv, nq, nk, d, nhd, stride triples of q, k, v and of a fresh output, dtype code) for
+    a call inside the envelope; raises the documented exception otherwise.  Pointer alignment is
+    part of the signature."""
+    key = (tensor_layout, q.shape, q.stride(), k.shape, k.stride(), v.shape, v.stride(), q.dtype, k.dtype,
+           v.dtype, q.device, k.device, v.device,
+           (q.data_ptr() | k.data_ptr() | v.data_ptr()) & 15)
+    hit = _sig_cache.get(key)
+    if hit is not None:
+        return hit
+    reason = envelope_reason(q, k, v, tensor_layout)
+    if reason is not None:
+        _counters["refusals"] += 1
+        if reason == "device" and not (q.is_cuda and k.is_cuda and v.is_cuda):
+            raise ValueError("sageattn (B200 path) needs CUDA tensors; there is no CPU path")
+        if reason == "head_dim":
+            raise NotImplementedError("sageattn (B200 path) serves head_dim 8..128 in multiples of 8")
+        raise ValueError("sageattn (B200 path) cannot serve this call: %s" % reason)
+    nhd = tensor_layout == "NHD"
+    qs, ks = q.shape, k.shape
+    if nhd:
+        b, nq, hq, d = qs
+        nk, hkv = ks[1], ks[2]
+    else:
+        b, hq, nq, d = qs
+        hkv, nk = ks[1], ks[2]
+    b, hq, hkv, nq, nk, d = int(b), int(hq), int(hkv), int(nq), int(nk), int(d)
+    # (batch, head, row) strides of a freshly allocated output with q's shape
+    o3 = _native.strides3(nq * hq * d, d, hq * d) if nhd else _native.strides3(hq * nq * d, nq * d, d)
+    val = (b, hq, hkv, nq, nk, d, nhd,
+           _native.strides3(*_logical_strides(q, nhd)), _native.strides3(*_logical_strides(k, nhd)),
+           _native.strides3(*_logical_strides(v, nhd)), o3, _dtype_code(q.dtype))
+    if len(_sig_cache) >= _SIG_CACHE_ENTRIES:
+        _sig_cache.clear()
+    _sig_cache[key] = val
+    return val
+
+
 def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smooth_k=True,
               int8: Optional[bool] = None, out: Optional[torch.Tensor] = None, return_lse: bool = False,
               smooth_v: bool = False):
@@ -236,48 +287,39 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     with q's shape, dtype and layout -- and, with `return_lse`, also the fp32 log-sum-exp
     (B, Hq, Nq).  `smooth_v` quantises V minus its sequence mean and adds the mean back to the
     output.  Raises ValueError for a call outside the envelope."""
-    reason = envelope_reason(q, k, v, tensor_layout)
-    with _counters_lock:
-        _counters["calls"] += 1
-        if reason is not None:
-            _counters["refusals"] += 1
-    if reason is not None:
-        if reason == "device" and not (q.is_cuda and k.is_cuda and v.is_cuda):
-            raise ValueError("sageattn (B200 path) needs CUDA tensors; there is no CPU path")
-        if reason == "head_dim":
-            raise NotImplementedError("sageattn (B200 path) serves head_dim 8..128 in multiples of 8")
-        raise ValueError("sageattn (B200 path) cannot serve this call: %s" % reason)
-    lib = _native.load()
-    if tensor_layout == "NHD":
-        ql, kl, vl = q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2)
-    else:
-        ql, kl, vl = q, k, v
-    b, h, n, d = ql.shape
-    hkv, nk = int(kl.shape[1]), int(kl.shape[2])
+    _counters["calls"] += 1
+    b, h, hkv, n, nk, d, nhd, q3, k3, v3, o3, dt = _validated(q, k, v, tensor_layout)
     if is_causal and nk != n:
         raise ValueError("sageattn (B200 path): a causal call needs q_len == kv_len")
+    lib = _native.load()
     dev = q.device
-    if sm_scale is None:
-        sm_scale = d ** -0.5
     if out is None:
         out = torch.empty(q.shape, dtype=q.dtype, device=dev)
-    ol = out.transpose(1, 2) if tensor_layout == "NHD" else out
-    if tuple(ol.shape) != (b, h, n, d) or out.dtype != q.dtype or strided_view_reason(ol) is not None:
-        raise ValueError("out must have q's shape and dtype and be a servable view")
+    else:
+        ol = out.transpose(1, 2) if nhd else out
+        if tuple(ol.shape) != (b, h, n, d) or out.dtype != q.dtype or strided_view_reason(ol) is not None:
+            raise ValueError("out must have q's shape and dtype and be a servable view")
+        o3 = _native.strides3(*_logical_strides(out, nhd))
+    if out.data_ptr() & 15:
+        raise ValueError("out must be 16-byte aligned")
     if int8 is None:
         qk_mode = -1
     else:
         qk_mode = _native.SAGE_QK_INT8 if int8 else _native.SAGE_QK_E4M3
-    stream = torch.cuda.current_stream(dev)
-    ws = _workspace(dev, int(stream.cuda_stream), b, h, n, hkv, nk)
+    stream_id = torch.cuda.current_stream(dev).cuda_stream
+    ws = _workspace(dev, stream_id, b, h, n, hkv, nk)
     lse = torch.empty((b, h, n), dtype=torch.float32, device=dev) if return_lse else None
-    with torch.cuda.device(dev):
-        rc = lib.sage_attention_ex(
-            _ptr(ql), _ptr(kl), _ptr(vl), _ptr(ol), _ptr(lse), _ptr(ws), ws.numel(), b, h, hkv, n, nk, d,
-            _bhr(ql), _bhr(kl), _bhr(vl), _bhr(ol), _dtype_code(q.dtype), qk_mode,
-            1 if is_causal else 0, 1 if smooth_k else 0, 1 if smooth_v else 0, float(sm_scale),
-            ctypes.c_void_p(int(stream.cuda_stream)))
-    _native.check(rc, "sage_attention_ex")
+    args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 0 if lse is None else lse.data_ptr(),
+            ws.data_ptr(), ws.numel(), b, h, hkv, n, nk, d, q3, k3, v3, o3, dt, qk_mode,
+            1 if is_causal else 0, 1 if smooth_k else 0, 1 if smooth_v else 0,
+            d ** -0.5 if sm_scale is None else float(sm_scale), stream_id)
+    if torch.cuda.current_device() == dev.index:
+        rc = lib.sage_attention_ex(*args)
+    else:
+        with torch.cuda.device(dev):
+            rc = lib.sage_attention_ex(*args)
+    if rc:
+        _native.check(rc, "sage_attention_ex")
     if return_lse:
         return out, lse
     return out

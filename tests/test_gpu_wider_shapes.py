@@ -192,3 +192,26 @@ def test_varlen_matches_per_sequence_calls(dtype, causal):
         ref = R.sdpa_fp32(q[a:b].transpose(0, 1).unsqueeze(0).cpu(), k[c:d].transpose(0, 1).unsqueeze(0).cpu(),
                           v[c:d].transpose(0, 1).unsqueeze(0).cpu(), is_causal=causal)
         assert R.rel_rms(out[a:b].transpose(0, 1).unsqueeze(0).cpu(), ref) < MAX_REL_RMS
+
+
+def test_cuda_graph_capture_and_replay():
+    """After one warm-up call (library load, shared-memory opt-in, workspace allocation) the whole
+    call -- memsets, tensor-map encodes on the host, three kernels -- can be captured and replayed."""
+    q, k, v = _inputs(1, 8, 8, 300, 300, torch.float16, 11)
+    q, k, v = q.cuda(), k.cuda(), v.cuda()
+    want = sageattention.sageattn(q, k, v, is_causal=True)
+    s = torch.cuda.Stream()
+    s.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(s):
+        sageattention.sageattn(q, k, v, is_causal=True)          # warm-up on the capture stream
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g, stream=s):
+            got = sageattention.sageattn(q, k, v, is_causal=True)
+    torch.cuda.current_stream().wait_stream(s)
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(got, want)
+    q.copy_(torch.roll(q, 1, dims=2))                              # new data in the captured buffers
+    g.replay()
+    torch.cuda.synchronize()
+    assert torch.equal(got, sageattention.sageattn(q, k, v, is_causal=True))
