@@ -194,7 +194,8 @@ int sage_workspace_layout_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int
                              size_t offsets[13]);
 
 /* Offsets (bytes from `workspace`) of the intermediates sage_attention uses, for callers and
- * tests that want to look at them: order q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status.
+ * tests that want to look at them: order q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status
+ * (the status word is a spare word inside the ctrl block, so that one memset clears both).
  * Returns the number of entries written (11). */
 int sage_workspace_layout(int64_t B, int64_t H, int64_t N, size_t offsets[11]);
 

@@ -107,7 +107,9 @@ Layout carve(const Dims& d) {
   L.s_fold = take(bhk * 4);
   L.mean = take(bhk * sage::HD * 4);
   L.ctrl = take(sage::prologue_ctrl_bytes(d.B, d.Hkv, d.Nk));
-  L.status = take(256);
+  // the attention kernel's status word is the spare word of the control header, so that the
+  // prologue's one memset clears it too
+  L.status = L.ctrl + 4 * (sage::CtrlHeader::status_word((int64_t)bhk) + 1);
   L.qm = take(bhq * nq * 4);
   L.vmean = take(bhk * sage::HD * 4);
   L.total = off;
@@ -194,9 +196,7 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
   if (qk_mode < 0) qk_mode = (dtype == SAGE_BF16) ? SAGE_QK_E4M3 : SAGE_QK_INT8;
   char* w = reinterpret_cast<char*>(workspace);
   const int64_t Nk_pad = sage_pad_len(d.Nk);
-  int32_t* status = reinterpret_cast<int32_t*>(w + L.status);
-  cudaError_t e = cudaMemsetAsync(status, 0, 4, reinterpret_cast<cudaStream_t>(stream));
-  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s", who, cudaGetErrorString(e));
+  int32_t* status = reinterpret_cast<int32_t*>(w + L.status);     // zeroed by the prologue's memset
   float* qm = (lse && smooth_k) ? reinterpret_cast<float*>(w + L.qm) : nullptr;
   float* vmean = smooth_v ? reinterpret_cast<float*>(w + L.vmean) : nullptr;
   rc = prologue_impl(q, k, v, w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
