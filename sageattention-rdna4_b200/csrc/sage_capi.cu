@@ -64,6 +64,7 @@ int check_strides(const char* name, const int64_t s[3]) {
   for (int i = 0; i < 3; ++i) {
     if (s[i] <= 0) return fail(SAGE_E_ARG, "%s stride %d is not positive", name, i);
     if (s[i] % 8) return fail(SAGE_E_ARG, "%s stride %d is not a multiple of 8 elements", name, i);
+    if (s[i] >= ((int64_t)1 << 39)) return fail(SAGE_E_UNSUPPORTED, "%s stride %d exceeds 2^39 elements", name, i);
   }
   return SAGE_OK;
 }

@@ -22,11 +22,13 @@ from . import _native
 
 HEAD_DIM = 128
 TILE = 128
-_INT32_MAX = 2 ** 31 - 1
+_STRIDE_MAX = 2 ** 39 - 1          # elements: a tensor map takes byte strides below 2**40
 
-#: Every reason `strided_view_reason` can return, in evaluation order (same strings as the reference).
+#: Every reason `strided_view_reason` can return, in evaluation order (the reference's strings, but
+#: "stride_range" where the reference has "stride_int32": its kernels index with 32-bit strides,
+#: these take 64-bit ones, so that a batch of long sequences does not have to be split).
 STRIDED_REFUSALS = ("rank", "stride_last", "stride_nonpos", "stride_align", "ptr_align",
-                    "stride_overlap", "stride_int32")
+                    "stride_overlap", "stride_range")
 
 _counters = {"calls": 0, "refusals": 0}
 
@@ -39,7 +41,7 @@ def strided_view_reason(t: torch.Tensor) -> Optional[str]:
     """None if `t` is a servable logical (B,H,N,D) view, else the reason.  Same rule and order as
     the reference: rank 4; last stride 1; strides positive; outer strides multiples of 8 elements;
     16-byte aligned pointer; injective index map (dims of size > 1 sorted by stride must satisfy
-    stride[k+1] >= stride[k]*size[k]); strides below 2**31."""
+    stride[k+1] >= stride[k]*size[k]); strides below 2**39 elements (the reference: 2**31)."""
     if t.dim() != 4:
         return "rank"
     if int(t.stride(3)) != 1:
@@ -56,8 +58,8 @@ def strided_view_reason(t: torch.Tensor) -> Optional[str]:
     for (s0, n0), (s1, _n1) in zip(dims, dims[1:]):
         if s1 < s0 * n0:
             return "stride_overlap"
-    if any(s > _INT32_MAX for s in st):
-        return "stride_int32"
+    if any(s > _STRIDE_MAX for s in st):
+        return "stride_range"
     return None
 
 

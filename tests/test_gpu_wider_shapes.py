@@ -215,3 +215,27 @@ def test_cuda_graph_capture_and_replay():
     g.replay()
     torch.cuda.synchronize()
     assert torch.equal(got, sageattention.sageattn(q, k, v, is_causal=True))
+
+
+def test_strides_beyond_32_bits():
+    """Two batch elements more than 2**31 elements apart (the reference refuses such views; the
+    kernels here take 64-bit strides): same bits as the call on compact copies."""
+    far = 2 ** 31 + 4096
+    n, h = 200, 2
+    g = torch.Generator(device="cuda").manual_seed(5)
+
+    def spread():
+        buf = torch.empty(far + h * n * 128, dtype=torch.float16, device="cuda")
+        view = buf.as_strided((2, h, n, 128), (far, n * 128, 128, 1))
+        view.copy_(torch.randn(2, h, n, 128, device="cuda", generator=g).half())
+        return view
+
+    q, k, v = spread(), spread(), spread()
+    assert q.stride(0) > 2 ** 31
+    out = sageattention.sageattn(q, k, v, is_causal=True)
+    want = sageattention.sageattn(q.contiguous(), k.contiguous(), v.contiguous(), is_causal=True)
+    assert torch.equal(out, want)
+    out_far = torch.empty(far + h * n * 128, dtype=torch.float16, device="cuda").as_strided(
+        (2, h, n, 128), (far, n * 128, 128, 1))
+    be.sage_call(q, k, v, is_causal=True, out=out_far)
+    assert torch.equal(out_far, want)
