@@ -282,6 +282,7 @@ __global__ void __launch_bounds__(ATT_THREADS, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
   extern __shared__ uint8_t smem_raw[];
+  wait_for_predecessor();            // the quantised operands and the status word
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
   uint8_t* gbase = smem_raw + (base - raw_addr);
@@ -680,8 +681,7 @@ static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, con
     if (attr.numRegs * ATT_THREADS < 128 * REGS_PRODUCER + 256 * REGS_SOFTMAX) return cudaErrorLaunchOutOfResources;
     if (dev >= 0 && dev < 64) opted_in[dev] = true;
   }
-  kern<<<grid, ATT_THREADS, SMEM_BYTES, st>>>(mq, mk, mv, ka);
-  return cudaGetLastError();
+  return launch_after_predecessor(kern, grid, dim3(ATT_THREADS), SMEM_BYTES, st, mq, mk, mv, ka);
 }
 
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why) {

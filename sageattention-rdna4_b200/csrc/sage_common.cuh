@@ -30,6 +30,29 @@ struct CtrlHeader {
   }
 };
 
+// Programmatic dependent launch.  A kernel launched with launch_after_predecessor() may be placed
+// on the GPU while the kernel before it on the stream is still draining; it must call
+// wait_for_predecessor() before it touches anything that kernel (or anything earlier on the
+// stream) wrote.  allow_successor() in the earlier kernel says "my CTAs are all resident, the
+// next kernel's may be scheduled as mine retire".  Without the launch attribute both calls are
+// no-ops, so the kernels behave the same under a plain launch.
+#ifdef __CUDACC__
+__device__ __forceinline__ void wait_for_predecessor() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void allow_successor() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_after_predecessor(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                            cudaStream_t st, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr; cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#endif
+
 // How many CTAs share one head's sequence in the mean kernel.
 inline int kmean_splits(int64_t bh, int64_t n) {
   int64_t want = (4 * 148) / bh;                   // one full wave: four resident CTAs on each of 148 SMs

@@ -40,6 +40,7 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
              long long sb, long long sh, long long sr, int nsplit, long long chunk, int D) {
   __shared__ double red[16][HD];
   __shared__ int s_last;
+  allow_successor();                 // one wave: every CTA of this grid is resident
   const int tid = threadIdx.x, c = tid & 15, r = tid >> 4;
   const int split = blockIdx.x, bh = blockIdx.y;
   const long long b = bh / H, h = bh - b * H;
@@ -164,6 +165,8 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                      const __grid_constant__ CUtensorMap tm_v, const QuantArgs a) {
   extern __shared__ uint8_t qt_smem[];
   __shared__ long long s_item[QT_STAGES];
+  wait_for_predecessor();            // the means and the cleared control block
+  allow_successor();                 // persistent grid: every CTA is resident
   constexpr float QMAX = INT8 ? I8_MAX : F8_MAX;
   constexpr int QDIV = INT8 ? 127 : 448;
 
@@ -587,8 +590,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     if (e != cudaSuccess) return e;
     opted_in[dev][p.qk_mode == 0] = true;
   }
-  kern<<<(unsigned)ctas, 256, QT_SMEM_BYTES, st>>>(mq, mk, mv, a);
-  return cudaGetLastError();
+  return launch_after_predecessor(kern, dim3((unsigned)ctas), dim3(256), QT_SMEM_BYTES, st, mq, mk, mv, a);
 }
 
 cudaError_t launch_prologue(const PrologueParams& p, cudaStream_t st) {
