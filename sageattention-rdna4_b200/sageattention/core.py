@@ -8,12 +8,33 @@ Anything else raises -- there is no second backend to fall back to.
 """
 from __future__ import annotations
 
+import os
 import warnings
 from typing import Any, Optional
 
 import torch
 
 from . import b200_backend as _be
+
+
+def _env_switch(name: str) -> Optional[bool]:
+    """`1/true/yes/on` -> True, `0/false/no/off` -> False, anything else -> None; the reference's
+    reading of its `SAGEATTN_SK1_*` switches (sageattention/sk1_backend/__init__.py:284-297)."""
+    val = os.environ.get(name, "").strip().lower()
+    if val in ("1", "true", "yes", "on"):
+        return True
+    if val in ("0", "false", "no", "off"):
+        return False
+    return None
+
+
+# The reference's environment switches that still mean something here, read once at import like
+# there (sageattention/sk1_backend/__init__.py:48-57):
+#   SAGEATTN_SK1_INT8=0     float16 calls use e4m3 Q.K codes unless `sk1_int8` says otherwise
+#   SAGEATTN_SK1_BACKEND=0  asks for the other backends, which this package does not have: calls raise
+# (SAGEATTN_SK1_BF16, _PROLOGUE and _GFX1200 select AMD-side objects and have no meaning here.)
+SK1_INT8 = _env_switch("SAGEATTN_SK1_INT8") is not False
+SK1_BACKEND = _env_switch("SAGEATTN_SK1_BACKEND") is not False
 
 
 def _reject_common(return_lse: bool, kwargs: dict):
@@ -60,11 +81,15 @@ def sageattn(
     Returns a tensor with q's shape, dtype and layout (and the LSE when asked for).
     """
     _reject_common(return_lse, kwargs)
-    if sk1_backend is False or sk1_bf16 is False and q.dtype == torch.bfloat16:
+    if sk1_backend is False or (sk1_backend is None and not SK1_BACKEND) \
+            or sk1_bf16 is False and q.dtype == torch.bfloat16:
         raise NotImplementedError("sageattention (B200 path) has no alternative backend to switch to")
     int8 = None
-    if q.dtype == torch.float16 and sk1_int8 is not None:
-        int8 = bool(sk1_int8)
+    if q.dtype == torch.float16:
+        if sk1_int8 is not None:
+            int8 = bool(sk1_int8)
+        elif not SK1_INT8:
+            int8 = False
     return _be.sage_call(q, k, v, tensor_layout=tensor_layout, is_causal=bool(is_causal),
                          sm_scale=sm_scale, smooth_k=bool(kwargs.get("smooth_k", True)), int8=int8,
                          return_lse=bool(return_lse), smooth_v=bool(kwargs.get("smooth_v", False)))

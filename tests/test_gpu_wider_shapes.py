@@ -239,3 +239,23 @@ def test_strides_beyond_32_bits():
         (2, h, n, 128), (far, n * 128, 128, 1))
     be.sage_call(q, k, v, is_causal=True, out=out_far)
     assert torch.equal(out_far, want)
+
+
+def test_int8_environment_switch_selects_the_e4m3_kernel(tmp_path):
+    """SAGEATTN_SK1_INT8=0 in a fresh interpreter gives the e4m3 Q.K path bit for bit (the reference's
+    tests/test_sk1_backend.py:121-130)."""
+    import os
+    import subprocess
+    import sys
+    from conftest import ROOT
+    out_file = tmp_path / "o.pt"
+    code = ("import sys, torch; sys.path.insert(0, %r); sys.path.insert(0, %r); import sageattention as s; "
+            "from oracle import ref_numerics as R; q, k, v = R.make_inputs(1, 2, 300, seed=31, device='cuda'); "
+            "torch.save(s.sageattn(q, k, v).cpu(), %r)"
+            % (os.path.join(ROOT, "sageattention-rdna4_b200"), ROOT, str(out_file)))
+    res = subprocess.run([sys.executable, "-c", code], env=dict(os.environ, SAGEATTN_SK1_INT8="0"),
+                         capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    q, k, v = R.make_inputs(1, 2, 300, seed=31, device="cuda")
+    assert torch.equal(torch.load(out_file), sageattention.sageattn(q, k, v, sk1_int8=False).cpu())
+    assert not torch.equal(torch.load(out_file), sageattention.sageattn(q, k, v).cpu())

@@ -1,5 +1,6 @@
 """Host-side contract of the drop-in package: signatures, acceptance rule, refusals (CPU only)."""
 import inspect
+import os
 
 import pytest
 import torch
@@ -127,3 +128,25 @@ def test_varlen_argument_checks():
 
 def test_pad_len():
     assert [be.pad_len(n) for n in (1, 127, 128, 129, 8771, 47520)] == [128, 128, 128, 256, 8832, 47616]
+
+
+def test_environment_switches_are_read_at_import():
+    """SAGEATTN_SK1_BACKEND=0 asks for a backend this package does not have; SAGEATTN_SK1_INT8=0 makes
+    e4m3 Q.K the default for float16 (both read once, at import, like the reference)."""
+    import subprocess
+    import sys
+    from conftest import ROOT
+    code = ("import sys, torch; sys.path.insert(0, %r); import sageattention as s; from sageattention import core; "
+            "print(core.SK1_INT8, core.SK1_BACKEND); q = torch.zeros(1, 1, 4, 128, dtype=torch.float16); "
+            "s.sageattn(q, q, q)") % os.path.join(ROOT, "sageattention-rdna4_b200")
+
+    def run(env):
+        full = dict(os.environ, **env)
+        return subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, env=full, timeout=300)
+
+    off = run({"SAGEATTN_SK1_BACKEND": "0"})
+    assert off.stdout.split()[:2] == ["True", "False"] and "NotImplementedError" in off.stderr
+    fp8 = run({"SAGEATTN_SK1_INT8": "off"})
+    assert fp8.stdout.split()[:2] == ["False", "True"] and "no CPU path" in fp8.stderr
+    default = run({"SAGEATTN_SK1_INT8": "", "SAGEATTN_SK1_BACKEND": ""})
+    assert default.stdout.split()[:2] == ["True", "True"] and "no CPU path" in default.stderr
