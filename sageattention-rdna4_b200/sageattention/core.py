@@ -145,8 +145,9 @@ def sageattn_varlen(
 
     q : ``[cu_seqlens_q[-1], Hq, D]``; k, v : ``[cu_seqlens_k[-1], Hkv, D]``; ``cu_seqlens_*`` are
     int32 / int64 prefix sums of the sequence lengths (``[batch + 1]``).  Returns
-    ``[cu_seqlens_q[-1], Hq, D]``.  Each sequence is one call of the fixed-length kernels on a
-    strided view of the packed tensors (no copies), all on the current stream; the cumulative
+    ``[cu_seqlens_q[-1], Hq, D]``.  Each run of consecutive sequences with equal lengths is one
+    batched call of the fixed-length kernels on a strided view of the packed tensors (no copies),
+    all on the current stream; the cumulative
     lengths are read on the host, which synchronises once when they live on the device.
     `smooth_k` subtracts each sequence's own K mean (the reference subtracts the mean over the
     whole packed batch; softmax is invariant to either shift, only rounding differs).
@@ -173,12 +174,19 @@ def sageattn_varlen(
         if is_causal and nq != nk:
             raise ValueError("sequence %d: a causal call needs q_len == kv_len" % i)
     out = torch.empty_like(q)
-    for i in range(len(cq) - 1):
-        if cq[i + 1] == cq[i]:
-            continue
-        _be.sage_call(q[cq[i]:cq[i + 1]].unsqueeze(0), k[ck[i]:ck[i + 1]].unsqueeze(0),
-                      v[ck[i]:ck[i + 1]].unsqueeze(0), tensor_layout="NHD", is_causal=bool(is_causal),
-                      sm_scale=sm_scale, smooth_k=bool(smooth_k), out=out[cq[i]:cq[i + 1]].unsqueeze(0))
+    n_seq = len(cq) - 1
+    i = 0
+    while i < n_seq:
+        nq, nk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
+        j = i + 1                      # consecutive sequences of the same lengths go out as one batched call
+        while j < n_seq and cq[j + 1] - cq[j] == nq and ck[j + 1] - ck[j] == nk:
+            j += 1
+        if nq > 0:
+            run = j - i
+            _be.sage_call(q[cq[i]:cq[j]].unflatten(0, (run, nq)), k[ck[i]:ck[j]].unflatten(0, (run, nk)),
+                          v[ck[i]:ck[j]].unflatten(0, (run, nk)), tensor_layout="NHD", is_causal=bool(is_causal),
+                          sm_scale=sm_scale, smooth_k=bool(smooth_k), out=out[cq[i]:cq[j]].unflatten(0, (run, nq)))
+        i = j
     return out
 
 

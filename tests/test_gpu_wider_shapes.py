@@ -172,8 +172,8 @@ def test_smooth_v_mean_and_codes_match_the_oracle():
 @pytest.mark.parametrize("dtype,causal", [(torch.float16, False), (torch.bfloat16, True)])
 def test_varlen_matches_per_sequence_calls(dtype, causal):
     g = torch.Generator().manual_seed(8)
-    lens_q = [5, 130, 0, 257]
-    lens_k = lens_q if causal else [40, 130, 0, 64]
+    lens_q = [5, 130, 130, 130, 0, 257, 64, 64]            # runs of equal lengths go out as one batched call
+    lens_k = lens_q if causal else [40, 130, 130, 130, 0, 64, 200, 200]
     cu_q = torch.tensor([0] + list(torch.tensor(lens_q).cumsum(0)), dtype=torch.int32)
     cu_k = torch.tensor([0] + list(torch.tensor(lens_k).cumsum(0)), dtype=torch.int64).cuda()
     q = torch.randn(sum(lens_q), 4, 128, generator=g).to(dtype).cuda()
