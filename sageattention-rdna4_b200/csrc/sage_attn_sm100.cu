@@ -17,7 +17,9 @@
 //   p  = exp2(c_q*u - c_q*m); l = l*alpha + sum(p); P8 = e4m3(p * svp[key]) written to shared
 //        memory in the 128-byte swizzled K-major layout
 //   O += P8 . V8            kind::f8f6f4 into TMEM cols 128..255
-// Epilogue: out = O * (S_fold / (l * 448)) (+ mean of V with smooth_v) -> fp16 / bf16.
+// Epilogue: out = O * (S_fold / (l * 448)) (+ mean of V with smooth_v) -> fp16 / bf16, the first
+// head_dim columns of each row; optionally LSE = ln2 * (c_q*m + log2 l) + sm_scale * q.mean(K).
+// Grouped-query heads: the CTA of query head h reads the K/V tiles and scales of head h / group.
 // (numerics: kernels/hip/sk1_t6i.hip:151-299 and kernels/hip/sk1_t4a1sb.hip:176-189 of the
 // reference, with a 128-key instead of a 64-key tile for the running max; the two score factors
 // c_q and sk are applied one after the other instead of as one pre-multiplied factor, a
