@@ -124,6 +124,25 @@ def physical_gpu_index(local: int) -> int:
     return local
 
 
+def bind_near_gpu(phys_index: int) -> str:
+    """Run this process (and so first-touch its pinned host buffers) on the CPU cores next to its
+    GPU, as NVML reports them: with several ranks per host the end-to-end copies otherwise cross
+    the socket interconnect.  Only this process's CPU affinity changes; no GPU setting is touched."""
+    try:
+        import pynvml
+        pynvml.nvmlInit()
+        handle = pynvml.nvmlDeviceGetHandleByIndex(phys_index)
+        words = pynvml.nvmlDeviceGetCpuAffinity(handle, (os.cpu_count() + 63) // 64)
+        near = {64 * i + b for i, w in enumerate(words) for b in range(64) if (int(w) >> b) & 1}
+        near &= os.sched_getaffinity(0)
+        if near:
+            os.sched_setaffinity(0, near)
+            return "%d cores next to GPU %d" % (len(near), phys_index)
+        return "unchanged (no allowed core next to the GPU)"
+    except Exception as exc:          # NVML missing or affinity not permitted: measure as is
+        return "unchanged (%s)" % type(exc).__name__
+
+
 def make_workload(dtype=torch.float16):
     from oracle import ref_numerics as R   # input generator only; nothing of the oracle is timed here
     return R.make_inputs(B, H, N, D, dtype, seed=SEED, outlier_frac=0.001)
@@ -280,9 +299,15 @@ def main() -> int:
         dist.init_process_group("nccl", device_id=dev)
 
     causal = args.causal
-    q_h, k_h, v_h = (t.pin_memory() for t in make_workload())
-    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
+    workload = make_workload()
+    all_cores = os.sched_getaffinity(0)
+    affinity = bind_near_gpu(physical_gpu_index(local))      # the pinned buffers are first touched here
+    q_h, k_h, v_h = (t.pin_memory() for t in workload)
     out_h = torch.empty_like(q_h).pin_memory()
+    out_h_alt = torch.empty_like(q_h).pin_memory()
+    os.sched_setaffinity(0, all_cores)                       # everything else (CPU baseline included) as before
+    del workload
+    q, k, v = q_h.to(dev), k_h.to(dev), v_h.to(dev)
     stream = torch.cuda.current_stream(dev)
 
     def sync_all():
@@ -384,7 +409,7 @@ def main() -> int:
     bufs = [tuple(torch.empty_like(q) for _ in range(3)) for _ in range(2)]
     ev_in = [[torch.cuda.Event() for _ in range(GROUPS)] for _ in range(2)]
     ev_cmp = [[torch.cuda.Event() for _ in range(GROUPS)] for _ in range(2)]
-    out_h2 = [out_h, torch.empty_like(out_h).pin_memory()]
+    out_h2 = [out_h, out_h_alt]
 
     def pipelined(n_steps, first):
         for i in range(first, first + n_steps):
@@ -424,7 +449,7 @@ def main() -> int:
                h2d_bytes_per_step=3 * nbytes, d2h_bytes_per_step=nbytes,
                how="copy-in, copy-out and two compute streams, two sets of device buffers; a step is issued as %d "
                    "head groups through the public API so that copies of one group overlap the calls of the others" % GROUPS,
-               serial_ms_per_step=e2e_serial_ms,
+               host_affinity=affinity, serial_ms_per_step=e2e_serial_ms,
                serial_value=flops(causal, B * world) / (e2e_serial_ms * 1e-3) / 1e12)
 
     # ---- the other arms of the configurations (informative; N = 1 only) ----
