@@ -259,3 +259,24 @@ def test_int8_environment_switch_selects_the_e4m3_kernel(tmp_path):
     q, k, v = R.make_inputs(1, 2, 300, seed=31, device="cuda")
     assert torch.equal(torch.load(out_file), sageattention.sageattn(q, k, v, sk1_int8=False).cpu())
     assert not torch.equal(torch.load(out_file), sageattention.sageattn(q, k, v).cpu())
+
+
+def test_caller_that_probes_for_attn_mask_and_passes_nhd():
+    """The way ComfyUI's `--use-sage-attention` drives the package: it inspects `sageattn` for an
+    `attn_mask` parameter (none, so masked calls stay with its own attention), reshapes to
+    (batch, tokens, heads, head_dim), and calls with `tensor_layout="NHD"`, `is_causal=False` and,
+    through its generic wrapper, `attn_mask=None`.  No ComfyUI here: this is the call pattern."""
+    import inspect
+    assert "attn_mask" not in inspect.signature(sageattention.sageattn).parameters
+    b, heads, dim_head, n = 2, 6, 128, 333
+    g = torch.Generator().manual_seed(12)
+    q, k, v = (torch.randn(b, n, heads * dim_head, generator=g).half().cuda() for _ in range(3))
+    q4, k4, v4 = (t.view(b, -1, heads, dim_head) for t in (q, k, v))
+    out = sageattention.sageattn(q4, k4, v4, attn_mask=None, is_causal=False, tensor_layout="NHD")
+    out = out.reshape(b, -1, heads * dim_head)
+    ref = torch.nn.functional.scaled_dot_product_attention(
+        q4.transpose(1, 2).float(), k4.transpose(1, 2).float(), v4.transpose(1, 2).float()).transpose(1, 2)
+    assert R.rel_rms(out.view(b, n, heads, dim_head).cpu(), ref.cpu()) < MAX_REL_RMS
+    with pytest.raises(NotImplementedError):
+        sageattention.sageattn(q4, k4, v4, attn_mask=torch.ones(n, n, device="cuda", dtype=torch.bool),
+                               tensor_layout="NHD")
