@@ -58,6 +58,8 @@ class GoldenCase:
         self.ref_sk = _from_bits(g("ref_sk"), torch.float32)
         self.ref_v8 = _from_bits(g("ref_v8"), torch.float8_e4m3fn)
         self.ref_sv = _from_bits(g("ref_sv"), torch.float32)
+        self.ref_S = _from_bits(g("ref_S"), torch.float32)               # the reference's fold_v_scale
+        self.ref_svfold = _from_bits(g("ref_svfold"), torch.float32)     # (B*H, N_pad), sv / S
         self.ora = {}
         for key, dt in (("q8", code), ("sq", torch.float32), ("k8", code), ("sk", torch.float32),
                         ("v8", torch.float8_e4m3fn), ("sv", torch.float32), ("svp", torch.float32),

@@ -4,9 +4,14 @@
 
 Two kinds of vectors are written to `quant_golden.npz`:
 
-* `ref_*`  -- produced by the REFERENCE's own PyTorch checkers `ref_quant_row_i8` and
-  `ref_quant_row_fp8` (sageattention/sk1_backend/quant_triton.py:1128-1156), imported from the
-  checkout given on the command line.  They pin the row quantisers of the oracle.
+* `ref_*`  -- produced by the REFERENCE's own PyTorch code, taken from the checkout given on the
+  command line: the checkers `ref_quant_row_i8` and `ref_quant_row_fp8`
+  (sageattention/sk1_backend/quant_triton.py:1128-1156, imported as a module) pin the row
+  quantisers of the oracle; `fold_v_scale` (sageattention/sk1_backend/__init__.py:561-579) and
+  `n_pad_for` (sageattention/sk1_backend/hip_prologue.py:93-95) are plain PyTorch / Python
+  functions inside modules that cannot be imported here (they load GPU objects at import), so
+  their source is cut out of the file and executed on its own; they pin the fold S, the folded
+  V scales and the reference's padded length.
 * `ora_*`  -- produced by the oracle (oracle/ref_numerics.py) on the same stored inputs: the whole
   prologue and the attention output.  They pin the CUDA path against a committed answer, so a GPU
   test needs neither the reference checkout nor a re-run of the oracle.
@@ -15,6 +20,7 @@ Inputs are stored in the file (not re-drawn from a seed) so the fixtures do not 
 random-number generator's version.
 """
 import argparse
+import ast
 import importlib.util
 import os
 import sys
@@ -47,6 +53,21 @@ def bits(t: torch.Tensor) -> np.ndarray:
     return t.numpy()
 
 
+def function_from_source(path: str, name: str):
+    """Compile one top-level function of a Python file without importing the file."""
+    src = open(path).read()
+    body = ast.parse(src).body
+    ns = {}
+    for node in body:                  # module-level literal constants the function may read (e.g. BN = 64)
+        if isinstance(node, ast.Assign) and isinstance(node.value, ast.Constant):
+            exec(compile(ast.get_source_segment(src, node), path, "exec"), ns)
+    for node in body:
+        if isinstance(node, ast.FunctionDef) and node.name == name:
+            exec(compile(ast.get_source_segment(src, node), path, "exec"), ns)
+            return ns[name]
+    raise KeyError(name)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--reference", required=True, help="path of the reference checkout")
@@ -56,7 +77,14 @@ def main() -> int:
     ref = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(ref)
 
+    backend = os.path.join(args.reference, "sageattention", "sk1_backend")
+    ref_fold = function_from_source(os.path.join(backend, "__init__.py"), "fold_v_scale")
+    ref_n_pad = function_from_source(os.path.join(backend, "hip_prologue.py"), "n_pad_for")
+
     out = {}
+    lengths = [1, 15, 63, 64, 65, 127, 128, 129, 300, 1000, 8771, 47520]
+    out["n_pad/N"] = np.array(lengths)
+    out["n_pad/ref"] = np.array([ref_n_pad(n) for n in lengths])
     for name, b, h, n, dtype, causal, smooth in CASES:
         q, k, v = R.make_inputs(b, h, n, 128, dtype, seed=1234 + n, k_bias_std=0.75)
         if n >= 65 and h >= 2:   # one |V| > 448 token so that S > 1, one all-zero K row, one large Q row
@@ -79,6 +107,9 @@ def main() -> int:
         out[p + "meta"] = np.array([b, h, n, int(dtype == torch.bfloat16), int(causal), int(smooth)])
         out[p + "ref_k8"], out[p + "ref_sk"] = bits(rk8), bits(rsk.float())
         out[p + "ref_v8"], out[p + "ref_sv"] = bits(rv8), bits(rsv.float())
+        folded = pq["sv"].reshape(b * h, -1).clone()          # the reference folds in place, (B*H, N_pad)
+        out[p + "ref_S"] = bits(ref_fold(folded).float())
+        out[p + "ref_svfold"] = bits(folded)
         for key in ("q8", "sq", "k8", "sk", "v8", "sv", "svp", "S"):
             out[p + "ora_" + key] = bits(pq[key])
         if smooth:

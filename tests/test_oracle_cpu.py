@@ -118,3 +118,20 @@ def test_tile128_close_to_tile64():
 def test_flops_formula():
     assert R.attention_flops(1, 48, 47520, 128, False) == pytest.approx(5.55e13, rel=1e-2)
     assert R.attention_flops(1, 48, 47520, 128, True) == pytest.approx(2.775e13, rel=1e-2)
+
+
+def test_fold_matches_the_reference_function(golden):
+    """S and sv / S of the oracle against the vectors produced by the reference's own
+    `fold_v_scale` (run from its source when the golden file was made), bit for bit; one of the
+    stored cases has a |V| > 448 token, so S > 1 is covered."""
+    g = golden
+    pq = R.prologue(g.q, g.k, g.v, smooth_k=g.smooth, int8=g.int8, pad_multiple=128)
+    bh = g.B * g.H
+    assert torch.equal(pq["S"].reshape(bh), g.ref_S)
+    assert torch.equal(pq["svp"].reshape(bh, -1), g.ref_svfold)
+
+
+def test_padded_length_matches_the_reference_function(golden_file):
+    """`pad_len(n, 64)` against the reference's `n_pad_for` for the edge lengths and the benchmark ones."""
+    for n, want in zip(golden_file["n_pad/N"], golden_file["n_pad/ref"]):
+        assert R.pad_len(int(n), 64) == int(want)
