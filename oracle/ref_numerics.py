@@ -19,9 +19,11 @@ Parity status: the reference ships no golden vectors for this path (its tests co
 SDPA with a tolerance).  The K/V row quantisers here are pinned against the reference's own
 PyTorch checkers `ref_quant_row_i8` / `ref_quant_row_fp8`
 (sageattention/sk1_backend/quant_triton.py:1128-1156), imported from the reference when the
-fixtures under tests/golden/ were generated.  The Q quantiser, the mean, the S fold and the
-attention loop have no runnable counterpart outside AMD hardware: for those parity is pinned by the
-source-level arithmetic only ("parity unpinned" by any reference-produced vector).
+fixtures under tests/golden/ were generated; the S fold and the padded length are pinned against
+the reference's own `fold_v_scale` and `n_pad_for`, whose source was executed at the same time.
+The Q quantiser, the mean and the attention loop have no runnable counterpart outside AMD
+hardware: for those parity is pinned by the source-level arithmetic only ("parity unpinned" by any
+reference-produced vector).
 
 All arithmetic is separate, correctly rounded fp32 operations unless stated; the code is plain
 torch so it runs on CPU (the oracle proper) and, unchanged, on a CUDA device when a test needs the
