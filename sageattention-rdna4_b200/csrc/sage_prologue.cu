@@ -54,7 +54,7 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
   const long long n_end = (8 * c < D) ? n1 : n0;   // columns past head_dim: nothing to read, mean 0
 #pragma unroll 8
   for (long long n = n0 + r; n < n_end; n += 16) {
-    const uint4 u = __ldg(reinterpret_cast<const uint4*>(base + n * sr));
+    const uint4 u = __ldcs(reinterpret_cast<const uint4*>(base + n * sr));   // streaming: read once here
     float x[8];
     unpack8<T>(u, x);
 #pragma unroll
