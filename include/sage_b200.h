@@ -60,7 +60,10 @@ size_t sage_prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
  *             a multiple of 8 and every base pointer 16-byte aligned.
  *   q8        (B*H, N, 128)      int8 | e4m3 codes of Q, one scale per token
  *   sq        (B*H, N)           fp32 dequant scale of Q: amax/127 (int8) or amax/448 (e4m3)
- *   k8        (B*H, N_pad, 128)  codes of K - mean; pad rows 0
+ *   k8        (B*H, N_pad, 128)  codes of K - mean; pad rows 0.  Row order: inside every block of
+ *                                16 keys, key 4c + j is stored in row 2c + j (j < 2) or
+ *                                8 + 2c + j - 2 (j = 2, 3), the order the attention kernel's
+ *                                TMEM loads want; sk, sv, svp and v8t are in key order
  *   sk        (B*H, N_pad)       fp32 scale of K; pad rows 1.0
  *   v8t       (B*H, 128, N_pad)  e4m3 codes of V, transposed; pad columns 0
  *   sv        (B*H, N_pad)       fp32 scale of V; pad rows 0.0

@@ -7,15 +7,17 @@
 //              V^T tiles
 //   warp 1     allocates 256 TMEM columns; one thread issues every tcgen05.mma
 //   warps 2-3  idle: they complete the first warpgroup, whose registers setmaxnreg hands over
-//   warps 4-11 softmax: two threads per query row (TMEM lane = row); warps 4-7 take key columns
-//              0..63 of the tile, warps 8-11 columns 64..127; a pair exchanges its row maximum
-//              through shared memory and a two-arrival mbarrier
+//   warps 4-11 softmax: a warp owns 16 query rows (TMEM lanes) and all 128 key columns, read with
+//              the 16-lane 16x256b shape: four threads share a row, each holds two rows, and a row
+//              maximum is two shuffles
 // Per key tile j:
 //   S  = Q8 . K8^T          kind::i8 (s32) or kind::f8f6f4 (f32), M=N=K=128, into TMEM cols 0..127
 //   u  = f32(S) * sk[key]; mask; row max m (in the u domain); s = c_q * u is the log2-domain score
 //   alpha = exp2(c_q*(m_old - m_new)); O *= alpha in TMEM when some row's max moved
 //   p  = exp2(c_q*u - c_q*m); l = l*alpha + sum(p); P8 = e4m3(p * svp[key]) written to shared
-//        memory in the 128-byte swizzled K-major layout
+//        memory in the 128-byte swizzled K-major layout, four keys (one 32-bit word) at a time
+// The rows of a K8 tile arrive permuted inside 16-row blocks (the prologue stores them so) to make
+// the four score columns a thread holds of a 16-column block four consecutive keys.
 //   O += P8 . V8            kind::f8f6f4 into TMEM cols 128..255
 // Epilogue: out = O * (S_fold / (l * 448)) (+ mean of V with smooth_v) -> fp16 / bf16, the first
 // head_dim columns of each row; optionally LSE = ln2 * (c_q*m + log2 l) + sm_scale * q.mean(K).
@@ -46,8 +48,7 @@ constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;  // 2 stages
 constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;
 constexpr uint32_t OFF_SK = OFF_P + TILE_BYTES;     // 4-slot ring of K scales (arrive with the K tile)
 constexpr uint32_t OFF_SV = OFF_SK + 4 * VEC_BYTES; // 4-slot ring of staged V factors (same barrier)
-constexpr uint32_t OFF_XCH = OFF_SV + 4 * VEC_BYTES;// [parity][half][row] floats exchanged by a row's two threads
-constexpr uint32_t OFF_BAR = OFF_XCH + 4 * VEC_BYTES;
+constexpr uint32_t OFF_BAR = OFF_SV + 4 * VEC_BYTES;
 constexpr uint32_t OFF_MISC = OFF_BAR + 192;
 constexpr uint32_t SMEM_USED = OFF_MISC + 64;
 constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;   // slack for the 1024-byte alignment
@@ -55,7 +56,7 @@ constexpr uint32_t TMEM_COLS = 256;
 constexpr uint32_t TMEM_O = 128;
 
 enum Bar { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SFREE = 10,
-           BAR_PF = 11, BAR_PV = 12, BAR_X = 13 /* 4: one per TMEM lane quarter */, BAR_COUNT = 17 };
+           BAR_PF = 11, BAR_PV = 12, BAR_COUNT = 13 };
 
 enum { ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_SOFTMAX = 4 };
 
@@ -173,40 +174,29 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
   }
 }
 
-// 32 lanes x 32 columns of 32-bit: thread t of the warp receives columns col..col+31 of its lane.
-__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* r) {
+// 16 lanes x 256 bits per repetition: thread t holds lanes t/4 (registers 4i, 4i+1) and t/4 + 8
+// (registers 4i+2, 4i+3), columns 8i + 2(t%4) and the next one; x8 = 64 columns, 32 registers.
+__device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t* r) {
   asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      "tcgen05.ld.sync.aligned.16x256b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
       : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t* r) {
+__device__ __forceinline__ void tmem_st_16x256b_x8(uint32_t taddr, const uint32_t* r) {
   asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%32], "
-      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
-      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
-        "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
-        "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]),
-        "r"(taddr) : "memory");
+      "tcgen05.st.sync.aligned.16x256b.x8.b32 [%32], {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31};"
+      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]), "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tmem_ld8(uint32_t taddr, uint32_t* r) {
-  asm volatile(
-      "tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
-      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7])
-      : "r"(taddr) : "memory");
+__device__ __forceinline__ void tmem_ld_16x256b_x16(uint32_t taddr, uint32_t* r) {
+  tmem_ld_16x256b_x8(taddr, r);
+  tmem_ld_16x256b_x8(taddr + 64, r + 32);
 }
-__device__ __forceinline__ void tmem_st8(uint32_t taddr, const uint32_t* r) {
-  asm volatile(
-      "tcgen05.st.sync.aligned.32x32b.x8.b32 [%8], {%0, %1, %2, %3, %4, %5, %6, %7};"
-      ::"r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-        "r"(taddr) : "memory");
+__device__ __forceinline__ void tmem_st_16x256b_x16(uint32_t taddr, const uint32_t* r) {
+  tmem_st_16x256b_x8(taddr, r);
+  tmem_st_16x256b_x8(taddr + 64, r + 32);
+}
+__device__ __forceinline__ void sts32u(uint32_t addr, uint32_t v) {
+  asm volatile("st.shared.b32 [%0], %1;" ::"r"(addr), "r"(v) : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
@@ -220,15 +210,6 @@ __device__ __forceinline__ float4 lds128(uint32_t addr) {
 __device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
 }
-__device__ __forceinline__ float lds32(uint32_t addr) {
-  float v;
-  asm volatile("ld.shared.f32 %0, [%1];" : "=f"(v) : "r"(addr));
-  return v;
-}
-__device__ __forceinline__ void sts32(uint32_t addr, float v) {
-  asm volatile("st.shared.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
-}
-
 __device__ __forceinline__ float ex2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -311,7 +292,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     mbar_init(bar(BAR_SFREE), 8);
     mbar_init(bar(BAR_PF), 8);
     mbar_init(bar(BAR_PV), 1);
-    for (int q = 0; q < 4; ++q) mbar_init(bar(BAR_X + q), 2);
     misc[1] = (*reinterpret_cast<volatile int32_t*>(a.status) != 0) ? 1u : 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -396,28 +376,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       }
     } else if (warp >= 4) {
       // ------------------------------- softmax warps ------------------------------
+      // A warp owns 16 TMEM lanes (query rows) and all 128 key columns, read with the 16x256b
+      // shape: thread t holds rows r0 = t/4 and r0+8, and of every 8-column group the two columns
+      // 2c, 2c+1 (c = t%4).  K8 is stored with its rows permuted inside 16-row blocks so that the
+      // four columns a thread holds of a 16-column block are four CONSECUTIVE keys 16m+4c..+3:
+      // one 16-byte scale load serves both rows, the four e4m3 codes of a row are one 32-bit word of
+      // the P tile, and a row's maximum is two shuffles among the four threads that share it.
       asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
       const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
-      const int half = (warp - 4) >> 2;                     // which 64 key columns of the tile
-      const int row = 32 * quarter + lane;                  // TMEM lane == query row of the tile
-      const long long q_row = (long long)q_tile * TILE + row;
-      const uint32_t t_s = tmem + ((uint32_t)(32 * quarter) << 16) + 64 * half;
+      const int sub = (warp - 4) >> 2;                      // which 16 lanes of the quarter
+      const int r0 = lane >> 2, c = lane & 3;
+      const int lane_base = 32 * quarter + 16 * sub;
+      const int rowA = lane_base + r0, rowB = rowA + 8;     // this thread's two query rows of the tile
+      const long long q_rowA = (long long)q_tile * TILE + rowA, q_rowB = q_rowA + 8;
+      const uint32_t t_s = tmem + ((uint32_t)lane_base << 16);
       const uint32_t t_o = t_s + TMEM_O;
       // c_q = f32(f32(sm_scale * log2e) * sq); rows past N get 1 (their scores are all zero)
-      const float cq = (q_row < a.Nq)
-          ? __fmul_rn(__fmul_rn(a.sm_scale, LOG2E_F), __ldg(a.sq + (size_t)bh * a.Nq + q_row)) : 1.f;
-      const float2 cq2 = make_float2(cq, cq);
-      float m = -INFINITY, l = 0.f;
+      const float sl2 = __fmul_rn(a.sm_scale, LOG2E_F);
+      const float cqA = (q_rowA < a.Nq) ? __fmul_rn(sl2, __ldg(a.sq + (size_t)bh * a.Nq + q_rowA)) : 1.f;
+      const float cqB = (q_rowB < a.Nq) ? __fmul_rn(sl2, __ldg(a.sq + (size_t)bh * a.Nq + q_rowB)) : 1.f;
+      const float2 cqA2 = make_float2(cqA, cqA), cqB2 = make_float2(cqB, cqB);
+      float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
       bool ok = true;
-      // the four 16-byte chunks of this thread's half of the P row, in the 128-byte swizzle
-      const uint32_t p_row = base + OFF_P + row * 128;
-      const uint32_t swz = (uint32_t)(row & 7) << 4;
-      const uint32_t p_c0 = p_row + ((64u * half + 0u) ^ swz), p_c1 = p_row + ((64u * half + 16u) ^ swz);
-      const uint32_t p_c2 = p_row + ((64u * half + 32u) ^ swz), p_c3 = p_row + ((64u * half + 48u) ^ swz);
-      const uint32_t x_mine = base + OFF_XCH + 4u * (half * 128 + row);          // [parity][half][row]
-      const uint32_t x_other = base + OFF_XCH + 4u * ((half ^ 1) * 128 + row);
-      const uint32_t sk_half = base + OFF_SK + 256u * half;
-      const uint32_t xbar = bar(BAR_X + quarter);
+      // P tile: row r at r*128, 16-byte chunk m at (16m) ^ ((r & 7) << 4); rowA & 7 == rowB & 7 == r0
+      const uint32_t swz = (uint32_t)r0 << 4;
+      const uint32_t pA = base + OFF_P + (uint32_t)rowA * 128u + 4u * (uint32_t)c, pB = pA + 8u * 128u;
+      const uint32_t sk_c = base + OFF_SK + 16u * (uint32_t)c;   // scales of keys 16m+4c..+3 at + 64m
 
       for (int j = 0; j < n_tiles; ++j) {
         // S(j) complete implies the K stage, and with it this tile's scale rows, has landed
@@ -425,77 +409,91 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
-        uint32_t acc[64];
-        tmem_ld32(t_s, acc);
-        tmem_ld32(t_s + 32, acc + 32);
+        uint32_t acc[64];                                   // acc[8m + {0,1,4,5}]: row A keys +0..3; {2,3,6,7}: row B
+        tmem_ld_16x256b_x16(t_s, acc);
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
         mbar_arrive_lane0(bar(BAR_SFREE), lane);
         if (a.dbg != nullptr && j == a.dbg_tile) {
-          uint32_t* d = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + row) * TILE + 64 * half;
+          uint32_t* dA = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + rowA) * TILE + 4 * c;
+          uint32_t* dB = dA + 8 * TILE;
 #pragma unroll
-          for (int k = 0; k < 64; ++k) d[k] = acc[k];
+          for (int m = 0; m < 8; ++m) {
+            dA[16 * m + 0] = acc[8 * m + 0]; dA[16 * m + 1] = acc[8 * m + 1];
+            dA[16 * m + 2] = acc[8 * m + 4]; dA[16 * m + 3] = acc[8 * m + 5];
+            dB[16 * m + 0] = acc[8 * m + 2]; dB[16 * m + 1] = acc[8 * m + 3];
+            dB[16 * m + 2] = acc[8 * m + 6]; dB[16 * m + 3] = acc[8 * m + 7];
+          }
         }
 
-        const uint32_t skv = sk_half + (uint32_t)(j & 3) * VEC_BYTES;     // this tile's 64 K scales
-        const uint32_t svv = skv + (OFF_SV - OFF_SK);                      // and its 64 staged V factors
-        float2 u[32];                                       // u[i] = scores of keys 2i, 2i+1 (times sk)
+        const uint32_t skv = sk_c + (uint32_t)(j & 3) * VEC_BYTES;        // this tile's K scales
+        const uint32_t svv = skv + (OFF_SV - OFF_SK);                      // and its staged V factors
+        float2 uA[16], uB[16];                              // u[2m], u[2m+1]: keys 16m+4c+{0,1}, +{2,3} (times sk)
 #pragma unroll
-        for (int k4 = 0; k4 < 16; ++k4) {
-          const float4 kk = lds128(skv + 16 * k4);
-          float f0, f1, f2, f3;
+        for (int m = 0; m < 8; ++m) {
+          const float4 kk = lds128(skv + 64 * m);
+          float a0, a1, a2, a3, b0, b1, b2, b3;
           if (INT8) {
-            f0 = (float)(int)acc[4 * k4 + 0]; f1 = (float)(int)acc[4 * k4 + 1];
-            f2 = (float)(int)acc[4 * k4 + 2]; f3 = (float)(int)acc[4 * k4 + 3];
+            a0 = (float)(int)acc[8 * m + 0]; a1 = (float)(int)acc[8 * m + 1];
+            b0 = (float)(int)acc[8 * m + 2]; b1 = (float)(int)acc[8 * m + 3];
+            a2 = (float)(int)acc[8 * m + 4]; a3 = (float)(int)acc[8 * m + 5];
+            b2 = (float)(int)acc[8 * m + 6]; b3 = (float)(int)acc[8 * m + 7];
           } else {
-            f0 = __uint_as_float(acc[4 * k4 + 0]); f1 = __uint_as_float(acc[4 * k4 + 1]);
-            f2 = __uint_as_float(acc[4 * k4 + 2]); f3 = __uint_as_float(acc[4 * k4 + 3]);
+            a0 = __uint_as_float(acc[8 * m + 0]); a1 = __uint_as_float(acc[8 * m + 1]);
+            b0 = __uint_as_float(acc[8 * m + 2]); b1 = __uint_as_float(acc[8 * m + 3]);
+            a2 = __uint_as_float(acc[8 * m + 4]); a3 = __uint_as_float(acc[8 * m + 5]);
+            b2 = __uint_as_float(acc[8 * m + 6]); b3 = __uint_as_float(acc[8 * m + 7]);
           }
-          u[2 * k4 + 0] = __fmul2_rn(make_float2(f0, f1), make_float2(kk.x, kk.y));
-          u[2 * k4 + 1] = __fmul2_rn(make_float2(f2, f3), make_float2(kk.z, kk.w));
+          const float2 k01 = make_float2(kk.x, kk.y), k23 = make_float2(kk.z, kk.w);
+          uA[2 * m + 0] = __fmul2_rn(make_float2(a0, a1), k01);
+          uA[2 * m + 1] = __fmul2_rn(make_float2(a2, a3), k23);
+          uB[2 * m + 0] = __fmul2_rn(make_float2(b0, b1), k01);
+          uB[2 * m + 1] = __fmul2_rn(make_float2(b2, b3), k23);
         }
         // Tile-uniform mask: the diagonal tile when causal, the ragged last tile otherwise.
         if (CAUSAL) {
           if (j == q_tile) {
-            const int lim = row - 64 * half;                // local column k is masked when k > lim
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (2 * i > lim) u[i].x = -INFINITY;
-              if (2 * i + 1 > lim) u[i].y = -INFINITY;
+            for (int i = 0; i < 16; ++i) {
+              const int key = 16 * (i >> 1) + 4 * c + 2 * (i & 1);        // tile-local key of u[i].x
+              if (key > rowA) uA[i].x = -INFINITY;
+              if (key + 1 > rowA) uA[i].y = -INFINITY;
+              if (key > rowB) uB[i].x = -INFINITY;
+              if (key + 1 > rowB) uB[i].y = -INFINITY;
             }
           }
         } else {
           if ((long long)(j + 1) * TILE > a.N) {
-            const int live = (int)(a.N - (long long)j * TILE) - 64 * half;   // local k >= live is masked
+            const int live = (int)(a.N - (long long)j * TILE);            // tile-local key >= live is masked
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-              if (2 * i >= live) u[i].x = -INFINITY;
-              if (2 * i + 1 >= live) u[i].y = -INFINITY;
+            for (int i = 0; i < 16; ++i) {
+              const int key = 16 * (i >> 1) + 4 * c + 2 * (i & 1);
+              if (key >= live) { uA[i].x = -INFINITY; uB[i].x = -INFINITY; }
+              if (key + 1 >= live) { uA[i].y = -INFINITY; uB[i].y = -INFINITY; }
             }
           }
         }
-        float mx0 = u[0].x, mx1 = u[0].y, mx2 = u[1].x, mx3 = u[1].y;
+        float xa0 = uA[0].x, xa1 = uA[0].y, xb0 = uB[0].x, xb1 = uB[0].y;
 #pragma unroll
-        for (int i = 2; i < 32; i += 4) {
-          mx0 = max3(mx0, u[i].x, u[i].y);
-          mx1 = max3(mx1, u[i + 1].x, u[i + 1].y);
-          if (i + 2 < 32) {
-            mx2 = max3(mx2, u[i + 2].x, u[i + 2].y);
-            mx3 = max3(mx3, u[i + 3].x, u[i + 3].y);
+        for (int i = 1; i < 16; i += 2) {
+          xa0 = max3(xa0, uA[i].x, uA[i].y);
+          xb0 = max3(xb0, uB[i].x, uB[i].y);
+          if (i + 1 < 16) {
+            xa1 = max3(xa1, uA[i + 1].x, uA[i + 1].y);
+            xb1 = max3(xb1, uB[i + 1].x, uB[i + 1].y);
           }
         }
-        const float mloc = fmaxf(max3(mx0, mx1, mx2), mx3);
-        // exchange with the thread that owns the other 64 columns of this row
-        sts32(x_mine + (uint32_t)(j & 1) * 1024u, mloc);
-        __syncwarp();
-        mbar_arrive_lane0(xbar, lane);
-        ok = mbar_wait(xbar, (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
-        ok = __all_sync(0xffffffffu, ok);
-        if (!ok) break;
-        const float m_new = max3(m, mloc, lds32(x_other + (uint32_t)(j & 1) * 1024u));
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = ex2(cq * (m - m_use));
+        float mxA = fmaxf(xa0, xa1), mxB = fmaxf(xb0, xb1);
+        // the four threads of a row are the four lanes that differ in their low two bits
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 1));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 1));
+        mxA = fmaxf(mxA, __shfl_xor_sync(0xffffffffu, mxA, 2));
+        mxB = fmaxf(mxB, __shfl_xor_sync(0xffffffffu, mxB, 2));
+        const float mA_new = fmaxf(mA, mxA), mB_new = fmaxf(mB, mxB);
+        const float mA_use = (mA_new == -INFINITY) ? 0.f : mA_new;
+        const float mB_use = (mB_new == -INFINITY) ? 0.f : mB_new;
+        const float alphaA = ex2(cqA * (mA - mA_use)), alphaB = ex2(cqB * (mB - mB_use));
 
         if (j > 0) {
           ok = mbar_wait(bar(BAR_PV), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
@@ -503,47 +501,52 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (!ok) break;
           tc_fence_after();
         }
-        // The accumulator is rescaled after the exponentials, when the score registers are free
-        // (two TMEM round trips of 32 columns); PV(j) is not issued before this warp arrives.
-        const bool rescale = (j > 0) && __any_sync(0xffffffffu, m_new > m);
-        m = m_new;
+        // The accumulator is rescaled after the exponentials, when the score registers are free;
+        // PV(j) is not issued before this warp arrives.
+        const bool rescale = (j > 0) && __any_sync(0xffffffffu, (mA_new > mA) || (mB_new > mB));
+        mA = mA_new; mB = mB_new;
 
-        const float nm = -(cq * m_use);
-        const float2 nm2 = make_float2(nm, nm);
-        float2 ps0 = make_float2(0.f, 0.f), ps1 = make_float2(0.f, 0.f);
+        const float nmA = -(cqA * mA_use), nmB = -(cqB * mB_use);
+        const float2 nmA2 = make_float2(nmA, nmA), nmB2 = make_float2(nmB, nmB);
+        float2 psA = make_float2(0.f, 0.f), psB = make_float2(0.f, 0.f);
 #pragma unroll
-        for (int cc = 0; cc < 4; ++cc) {                    // 16 keys = one 16-byte chunk of the P row
-          uint32_t w[4];
-#pragma unroll
-          for (int g = 0; g < 4; ++g) {
-            const float4 vv = lds128(svv + 16 * (4 * cc + g));
-            const float2 t0 = __ffma2_rn(u[8 * cc + 2 * g + 0], cq2, nm2);
-            const float2 t1 = __ffma2_rn(u[8 * cc + 2 * g + 1], cq2, nm2);
+        for (int m = 0; m < 8; ++m) {                       // 16 keys = one 16-byte chunk of a P row; 4 of them here
+          const float4 vv = lds128(svv + 64 * m);
+          const float2 v01 = make_float2(vv.x, vv.y), v23 = make_float2(vv.z, vv.w);
+          {
+            const float2 t0 = __ffma2_rn(uA[2 * m + 0], cqA2, nmA2);
+            const float2 t1 = __ffma2_rn(uA[2 * m + 1], cqA2, nmA2);
             const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
             const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
-            ps0 = __fadd2_rn(ps0, p01);
-            ps1 = __fadd2_rn(ps1, p23);
-            const float2 f01 = __fmul2_rn(p01, make_float2(vv.x, vv.y));
-            const float2 f23 = __fmul2_rn(p23, make_float2(vv.z, vv.w));
-            w[g] = e4m3x4_pack(f01.x, f01.y, f23.x, f23.y);
+            psA = __fadd2_rn(psA, __fadd2_rn(p01, p23));
+            const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
+            sts32u(pA + ((16u * (uint32_t)m) ^ swz), e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
           }
-          sts128(cc == 0 ? p_c0 : cc == 1 ? p_c1 : cc == 2 ? p_c2 : p_c3, w[0], w[1], w[2], w[3]);
+          {
+            const float2 t0 = __ffma2_rn(uB[2 * m + 0], cqB2, nmB2);
+            const float2 t1 = __ffma2_rn(uB[2 * m + 1], cqB2, nmB2);
+            const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
+            const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
+            psB = __fadd2_rn(psB, __fadd2_rn(p01, p23));
+            const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
+            sts32u(pB + ((16u * (uint32_t)m) ^ swz), e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
+          }
         }
-        l = l * alpha + ((ps0.x + ps0.y) + (ps1.x + ps1.y));
+        lA = lA * alphaA + (psA.x + psA.y);                 // this thread's quarter of the row sum
+        lB = lB * alphaB + (psB.x + psB.y);
         if (rescale) {
-          const float2 al2 = make_float2(alpha, alpha);
-#pragma unroll 1
-          for (int i = 0; i < 2; ++i) {
-            uint32_t o[32];
-            tmem_ld32(t_o + 32 * i, o);
-            tmem_ld_wait();
+          const float2 aA2 = make_float2(alphaA, alphaA), aB2 = make_float2(alphaB, alphaB);
+          uint32_t o[64];
+          tmem_ld_16x256b_x16(t_o, o);
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; e += 2) {
-              const float2 r = __fmul2_rn(make_float2(__uint_as_float(o[e]), __uint_as_float(o[e + 1])), al2);
-              o[e] = __float_as_uint(r.x); o[e + 1] = __float_as_uint(r.y);
-            }
-            tmem_st32(t_o + 32 * i, o);
+          for (int i = 0; i < 16; ++i) {
+            const float2 ra = __fmul2_rn(make_float2(__uint_as_float(o[4 * i + 0]), __uint_as_float(o[4 * i + 1])), aA2);
+            const float2 rb = __fmul2_rn(make_float2(__uint_as_float(o[4 * i + 2]), __uint_as_float(o[4 * i + 3])), aB2);
+            o[4 * i + 0] = __float_as_uint(ra.x); o[4 * i + 1] = __float_as_uint(ra.y);
+            o[4 * i + 2] = __float_as_uint(rb.x); o[4 * i + 3] = __float_as_uint(rb.y);
           }
+          tmem_st_16x256b_x16(t_o, o);
           tmem_st_wait();
         }
         fence_async_smem();
@@ -558,50 +561,44 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
-        // total row sum = the two halves' sums (both were scaled with the same running max)
-        sts32(x_mine + (uint32_t)(n_tiles & 1) * 1024u, l);
-        __syncwarp();
-        mbar_arrive_lane0(xbar, lane);
-        ok = mbar_wait(xbar, (uint32_t)n_tiles & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
-        ok = __all_sync(0xffffffffu, ok);
-        if (ok) l += lds32(x_other + (uint32_t)(n_tiles & 1) * 1024u);
-      }
-      if (ok) {
         tc_fence_after();
+        // total row sums: the four quarters were scaled with the same running maximum
+        lA += __shfl_xor_sync(0xffffffffu, lA, 1); lB += __shfl_xor_sync(0xffffffffu, lB, 1);
+        lA += __shfl_xor_sync(0xffffffffu, lA, 2); lB += __shfl_xor_sync(0xffffffffu, lB, 2);
         const float S = __ldg(a.s_fold + bh_kv);
-        const float inv = (l > 0.f) ? __fdiv_rn(S, __fmul_rn(l, F8_MAX)) : 0.f;
+        const float invA = (lA > 0.f) ? __fdiv_rn(S, __fmul_rn(lA, F8_MAX)) : 0.f;
+        const float invB = (lB > 0.f) ? __fdiv_rn(S, __fmul_rn(lB, F8_MAX)) : 0.f;
         const long long b = bh / a.Hq, h = bh - b * a.Hq;
-        if (a.lse != nullptr && half == 0 && q_row < a.Nq) {
+        if (a.lse != nullptr && c == 0) {
           // ln sum_k exp(q.k*sm_scale) = ln2 * (c_q*m + log2 l) (+ q.mean*sm_scale with smooth_k)
-          float v = (l > 0.f) ? 0.6931471805599453f * (cq * m + log2f(l)) : -INFINITY;
-          if (a.qm != nullptr) v += a.sm_scale * __ldg(a.qm + (size_t)bh * a.Nq + q_row);
-          a.lse[(size_t)bh * a.Nq + q_row] = v;
+          if (q_rowA < a.Nq) {
+            float v = (lA > 0.f) ? 0.6931471805599453f * (cqA * mA + log2f(lA)) : -INFINITY;
+            if (a.qm != nullptr) v += a.sm_scale * __ldg(a.qm + (size_t)bh * a.Nq + q_rowA);
+            a.lse[(size_t)bh * a.Nq + q_rowA] = v;
+          }
+          if (q_rowB < a.Nq) {
+            float v = (lB > 0.f) ? 0.6931471805599453f * (cqB * mB + log2f(lB)) : -INFINITY;
+            if (a.qm != nullptr) v += a.sm_scale * __ldg(a.qm + (size_t)bh * a.Nq + q_rowB);
+            a.lse[(size_t)bh * a.Nq + q_rowB] = v;
+          }
         }
-        OutT* orow = reinterpret_cast<OutT*>(a.out) + b * a.o_sb + h * a.o_sh + q_row * a.o_sr + 64 * half;
+        OutT* orowA = reinterpret_cast<OutT*>(a.out) + b * a.o_sb + h * a.o_sh + q_rowA * a.o_sr + 2 * c;
+        OutT* orowB = orowA + 8 * a.o_sr;
+        const float* vm = (a.vmean != nullptr) ? a.vmean + (size_t)bh_kv * HD + 2 * c : nullptr;
+        uint32_t o[64];
+        tmem_ld_16x256b_x16(t_o, o);
+        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-          uint32_t o[32];
-          tmem_ld32(t_o + 32 * i, o);
-          tmem_ld_wait();
-          if (q_row < a.Nq) {
-#pragma unroll
-            for (int g = 0; g < 4; ++g) {
-              float f[8];
-#pragma unroll
-              for (int e = 0; e < 8; ++e) f[e] = __uint_as_float(o[8 * g + e]) * inv;
-              if (a.vmean != nullptr) {             // smooth_v: the rows of P sum to one, so add the mean back
-                const float4* vm = reinterpret_cast<const float4*>(a.vmean + (size_t)bh_kv * HD + 64 * half + 32 * i + 8 * g);
-                const float4 v0 = __ldg(vm), v1 = __ldg(vm + 1);
-                f[0] += v0.x; f[1] += v0.y; f[2] += v0.z; f[3] += v0.w;
-                f[4] += v1.x; f[5] += v1.y; f[6] += v1.z; f[7] += v1.w;
-              }
-              uint4 w;
-              w.x = pack2<OutT>(f[0], f[1]);
-              w.y = pack2<OutT>(f[2], f[3]);
-              w.z = pack2<OutT>(f[4], f[5]);
-              w.w = pack2<OutT>(f[6], f[7]);
-              if (64 * half + 32 * i + 8 * g < a.D) *reinterpret_cast<uint4*>(orow + 32 * i + 8 * g) = w;
+        for (int i = 0; i < 16; ++i) {                      // channels 8i + 2c, 8i + 2c + 1
+          if (8 * i + 2 * c < a.D) {
+            float fa0 = __uint_as_float(o[4 * i + 0]) * invA, fa1 = __uint_as_float(o[4 * i + 1]) * invA;
+            float fb0 = __uint_as_float(o[4 * i + 2]) * invB, fb1 = __uint_as_float(o[4 * i + 3]) * invB;
+            if (vm != nullptr) {                            // smooth_v: the rows of P sum to one, so add the mean back
+              const float2 mu = __ldg(reinterpret_cast<const float2*>(vm + 8 * i));
+              fa0 += mu.x; fa1 += mu.y; fb0 += mu.x; fb1 += mu.y;
             }
+            if (q_rowA < a.Nq) *reinterpret_cast<uint32_t*>(orowA + 8 * i) = pack2<OutT>(fa0, fa1);
+            if (q_rowB < a.Nq) *reinterpret_cast<uint32_t*>(orowB + 8 * i) = pack2<OutT>(fb0, fb1);
           }
         }
       }

@@ -364,7 +364,11 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           w1.x = e4m3x4(y[8], y[9], y[10], y[11]); w1.y = e4m3x4(y[12], y[13], y[14], y[15]);
         }
         if (!live) { w0 = make_uint2(0u, 0u); w1 = w0; }
-        uint8_t* dst = a.k8 + ((size_t)bh * N_pad + nrow) * HD + 8 * c;
+        // rows are stored permuted inside 16-row blocks: key 4cc + jj of a block goes to row
+        // 2cc + jj (jj < 2) or 8 + 2cc + jj - 2, the order in which the attention kernel's
+        // 16-lane TMEM loads hand a thread four consecutive keys
+        const long long o16 = nrow & 15, srow = (nrow & ~15LL) | ((o16 & 2) ? 8 + 2 * (o16 >> 2) + (o16 & 1) : 2 * (o16 >> 2) + (o16 & 1));
+        uint8_t* dst = a.k8 + ((size_t)bh * N_pad + srow) * HD + 8 * c;
         *reinterpret_cast<uint2*>(dst) = w0;
         *reinterpret_cast<uint2*>(dst + 64) = w1;
         if (c == 0) a.sk[(size_t)bh * N_pad + nrow] = live ? sk : 1.0f;

@@ -133,10 +133,21 @@ def _require_cuda(*ts):
                              % t.device.type)
 
 
+def k8_row_order(n_pad: int, device="cpu") -> torch.Tensor:
+    """Where the prologue stores the K codes of each key: `k8[:, k8_row_order(n_pad)]` is K8 in
+    key order.  Inside every block of 16 keys, key 4c + j sits in row 2c + j (j < 2) or
+    8 + 2c + j - 2 (j >= 2): the order in which the attention kernel's 16-lane TMEM loads hand a
+    thread four consecutive keys of a score row.  Scales (sk, sv, svp) are in key order."""
+    key = torch.arange(int(n_pad), device=device)
+    o = key & 15
+    c, j = o >> 2, o & 3
+    return (key & ~15) | torch.where(j < 2, 2 * c + j, 8 + 2 * c + j - 2)
+
+
 def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool = True,
               int8: Optional[bool] = None, reuse: Optional[dict] = None) -> Dict[str, torch.Tensor]:
     """Run the prologue on logical (B,H,N,D) views and return every tensor it writes:
-    q8 (BH,N,D), sq (BH,N), k8 (BH,N_pad,D), sk (BH,N_pad), v8t (BH,D,N_pad), sv, svp (BH,N_pad),
+    q8 (BH,N,D), sq (BH,N), k8 (BH,N_pad,D; rows in `k8_row_order`), sk (BH,N_pad), v8t (BH,D,N_pad), sv, svp (BH,N_pad),
     S (BH,), mean (BH,D) or None.  `int8=None` follows the reference's default: int8 codes for
     fp16 inputs, e4m3 for bf16.  Code tensors are torch.int8 or torch.float8_e4m3fn.  `reuse` is a
     previous result for the same shapes whose buffers are written again instead of allocating."""

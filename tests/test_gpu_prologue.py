@@ -16,7 +16,8 @@ def _check_against(pq_gpu, pq_ref, n, smooth):
     flat = lambda t: t.reshape(bh, *t.shape[2:]).cpu()
     assert bytes_equal(pq_gpu["q8"], flat(pq_ref["q8"])), "q8"
     assert torch.equal(pq_gpu["sq"].cpu(), flat(pq_ref["sq"])), "sq"
-    assert bytes_equal(pq_gpu["k8"], flat(pq_ref["k8"])), "k8"
+    k8_key_order = pq_gpu["k8"].cpu()[:, be.k8_row_order(n_pad)]       # stored permuted inside 16-key blocks
+    assert bytes_equal(k8_key_order, flat(pq_ref["k8"])), "k8"
     assert torch.equal(pq_gpu["sk"].cpu(), flat(pq_ref["sk"])), "sk"
     v8t_ref = flat(pq_ref["v8"]).transpose(1, 2).contiguous()
     assert bytes_equal(pq_gpu["v8t"], v8t_ref), "v8t"
@@ -94,9 +95,10 @@ def test_full_size_properties():
     pq = be.quant_qkv(q, k, v)
     n, n_pad = 8771, 8832
     assert pq["n_pad"] == n_pad
-    assert torch.all(pq["k8"][:, n:] == 0) and torch.all(pq["sk"][:, n:] == 1.0)
+    k8 = pq["k8"][:, be.k8_row_order(n_pad, device="cuda")]           # key order
+    assert torch.all(k8[:, n:] == 0) and torch.all(pq["sk"][:, n:] == 1.0)
     assert torch.all(pq["v8t"].view(torch.uint8)[:, :, n:] == 0) and torch.all(pq["sv"][:, n:] == 0)
-    assert pq["k8"].abs().amax(dim=2)[:, :n].min().item() == 127      # every live row uses the range
+    assert k8.abs().amax(dim=2)[:, :n].min().item() == 127            # every live row uses the range
     assert pq["q8"].abs().amax(dim=2).min().item() == 127
     ref = R.prologue(q, k, v, pad_multiple=128)                       # torch ops on the device
     _check_against(pq, ref, n, True)
