@@ -38,8 +38,8 @@ B, H, N, D = 1, 48, 47520, 128
 SEED = 0
 METRIC = "attention TFLOPS (full call incl. quant) at H=48 N=47520 D=128"
 # DRAM bytes of one attention-kernel launch at this workload, from the ncu capture summarised in
-# profiles/attn_fwd_kernel_H16_N16384_fp16_noncausal.md (launch list at the full-size workload: 914 MB read + 553 MB written).
-ATTN_DRAM_TRAFFIC_BYTES = 1.467e9
+# profiles/attn_fwd_kernel_H16_N16384_fp16_noncausal.md (launch list at the full-size workload: 914 MB read + 554 MB written).
+ATTN_DRAM_TRAFFIC_BYTES = 1.468e9
 
 
 def flops(causal: bool, batch: int = B) -> float:
