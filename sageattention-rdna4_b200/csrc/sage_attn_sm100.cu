@@ -1,24 +1,32 @@
 // Quantised flash attention for B200 (sm_100a): tcgen05 tensor cores, TMEM accumulators, TMA tiles.
 //
-// One CTA owns 128 queries of one (batch, head) and streams 128-key tiles; two CTAs share an SM so
-// that one CTA's softmax overlaps the other's matrix products.  Roles inside a CTA (384 threads):
-//   warp 0     TMA producer: Q tile once, then a 2-deep ring of K tiles (each carrying that tile's
-//              128 K scales and 128 staged V factors into a 4-slot ring) and a 2-deep ring of
-//              V^T tiles
-//   warp 1     allocates 256 TMEM columns; one thread issues every tcgen05.mma
-//   warps 2-3  idle: they complete the first warpgroup, whose registers setmaxnreg hands over
-//   warps 4-11 softmax: a warp owns 16 query rows (TMEM lanes) and all 128 key columns, read with
-//              the 16-lane 16x256b shape: four threads share a row, each holds two rows, and a row
-//              maximum is two shuffles
+// A query tile is 128 queries of one (batch, head); it streams 128-key tiles.  The kernel comes in
+// two shapes (template parameter NQ, query tiles per CTA):
+//   NQ = 1   one query tile per CTA, 384 threads, two CTAs per SM, so that one CTA's softmax
+//            overlaps the other's matrix products.  Causal calls and calls too small to give every
+//            SM a two-tile CTA.
+//   NQ = 2   two neighbouring query tiles of a head per CTA, 640 threads, one CTA per SM: each K
+//            and V^T tile is loaded once for both, each query tile has its own softmax warps,
+//            TMEM columns, P tile and MMA-issuing thread.  Non-causal calls.
+// Both shapes compute every row with the same instructions in the same order.  Roles inside a CTA:
+//   warp 0     TMA producer: the Q tile(s) once, then a 2-deep ring of K tiles (each carrying that
+//              tile's 128 K scales and 128 staged V factors into a 4-slot ring) and a 2-deep ring
+//              of V^T tiles
+//   warp 1     allocates 256 x NQ TMEM columns; one thread issues the tcgen05.mma of query tile 0
+//   warp 2     NQ = 2: one thread issues the tcgen05.mma of query tile 1 (idle for NQ = 1)
+//   warp 3     idle: it completes the first warpgroup, whose registers setmaxnreg hands over
+//   warps 4-11 (and 12-19 for the second query tile) softmax: a warp owns 16 query rows (TMEM
+//              lanes) and all 128 key columns, read with the 16-lane 16x256b shape: four threads
+//              share a row, each holds two rows, and a row maximum is two shuffles
 // Per key tile j:
-//   S  = Q8 . K8^T          kind::i8 (s32) or kind::f8f6f4 (f32), M=N=K=128, into TMEM cols 0..127
+//   S  = Q8 . K8^T          kind::i8 (s32) or kind::f8f6f4 (f32), M=N=K=128, into 128 TMEM columns
 //   u  = f32(S) * sk[key]; mask; row max m (in the u domain); s = c_q * u is the log2-domain score
 //   alpha = exp2(c_q*(m_old - m_new)); O *= alpha in TMEM when some row's max moved
 //   p  = exp2(c_q*u - c_q*m); l = l*alpha + sum(p); P8 = e4m3(p * svp[key]) written to shared
-//        memory in the 128-byte swizzled K-major layout, four keys (one 32-bit word) at a time
+//        memory as unswizzled K-major core matrices, four keys (one 32-bit word) at a time
 // The rows of a K8 tile arrive permuted inside 16-row blocks (the prologue stores them so) to make
 // the four score columns a thread holds of a 16-column block four consecutive keys.
-//   O += P8 . V8            kind::f8f6f4 into TMEM cols 128..255
+//   O += P8 . V8            kind::f8f6f4 into 128 more TMEM columns
 // Epilogue: out = O * (S_fold / (l * 448)) (+ mean of V with smooth_v) -> fp16 / bf16, the first
 // head_dim columns of each row; optionally LSE = ln2 * (c_q*m + log2 l) + sm_scale * q.mean(K).
 // Grouped-query heads: the CTA of query head h reads the K/V tiles and scales of head h / group.
@@ -37,26 +45,39 @@
 
 namespace sage {
 
-constexpr int ATT_THREADS = 384;                    // 3 warpgroups: {TMA, MMA, 2 idle warps}, 2 x softmax
-constexpr int REGS_AT_LAUNCH = 80;                  // what __launch_bounds__(384, 2) yields
-constexpr int REGS_PRODUCER = 32, REGS_SOFTMAX = 104;   // after setmaxnreg
 constexpr uint32_t TILE_BYTES = TILE * HD;          // 16 KiB: 128 rows x 128 one-byte codes
 constexpr uint32_t VEC_BYTES = TILE * 4;            // 128 floats
-constexpr uint32_t OFF_Q = 0;
-constexpr uint32_t OFF_K = OFF_Q + TILE_BYTES;      // 2 stages
-constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;  // 2 stages
-constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;
-constexpr uint32_t OFF_SK = OFF_P + TILE_BYTES;     // 4-slot ring of K scales (arrive with the K tile)
-constexpr uint32_t OFF_SV = OFF_SK + 4 * VEC_BYTES; // 4-slot ring of staged V factors (same barrier)
-constexpr uint32_t OFF_BAR = OFF_SV + 4 * VEC_BYTES;
-constexpr uint32_t OFF_MISC = OFF_BAR + 192;
-constexpr uint32_t SMEM_USED = OFF_MISC + 64;
-constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;   // slack for the 1024-byte alignment
-constexpr uint32_t TMEM_COLS = 256;
-constexpr uint32_t TMEM_O = 128;
 
+// Threads, registers, shared memory and TMEM of a CTA that owns NQ query tiles.
+template <int NQ> struct Shape {
+  static constexpr int THREADS = 128 + 256 * NQ;    // {TMA, MMA, MMA or idle, idle} + 8 softmax warps per tile
+  static constexpr int CTAS_PER_SM = (NQ == 1) ? 2 : 1;
+  // what __launch_bounds__(THREADS, CTAS_PER_SM) yields: 65536 / (THREADS x CTAS_PER_SM), rounded
+  // down to a multiple of 8
+  static constexpr int REGS_AT_LAUNCH = (NQ == 1) ? 80 : 96;
+  static constexpr int REGS_PRODUCER = 32;                      // after setmaxnreg
+  static constexpr int REGS_SOFTMAX = (NQ == 1) ? 104 : 112;
+  static constexpr uint32_t OFF_Q = 0;
+  static constexpr uint32_t OFF_K = OFF_Q + NQ * TILE_BYTES;    // 2 stages
+  static constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;     // 2 stages
+  static constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;     // one P tile per query tile
+  static constexpr uint32_t OFF_SK = OFF_P + NQ * TILE_BYTES;   // 4-slot ring of K scales (arrive with the K tile)
+  static constexpr uint32_t OFF_SV = OFF_SK + 4 * VEC_BYTES;    // 4-slot ring of staged V factors (same barrier)
+  static constexpr uint32_t OFF_BAR = OFF_SV + 4 * VEC_BYTES;
+  static constexpr uint32_t OFF_MISC = OFF_BAR + 192;
+  static constexpr uint32_t SMEM_USED = OFF_MISC + 64;
+  static constexpr uint32_t SMEM_BYTES = SMEM_USED + 1024;      // slack for the 1024-byte alignment
+  static constexpr uint32_t TMEM_COLS = 256 * NQ;
+  // score and output columns of query tile g
+  __host__ __device__ static constexpr uint32_t tmem_s(int g) { return 128u * (uint32_t)g; }
+  __host__ __device__ static constexpr uint32_t tmem_o(int g) { return 128u * NQ + 128u * (uint32_t)g; }
+};
+
+// The K/V stage barriers are shared by the query tiles of a CTA; the last four repeat per query
+// tile (+ BAR_PER_TILE x g).
 enum Bar { BAR_Q = 0, BAR_KF = 1, BAR_KE = 3, BAR_VF = 5, BAR_VE = 7, BAR_SF = 9, BAR_SFREE = 10,
-           BAR_PF = 11, BAR_PV = 12, BAR_COUNT = 13 };
+           BAR_PF = 11, BAR_PV = 12, BAR_PER_TILE = 4, BAR_COUNT = 17 };
+static_assert(BAR_COUNT * 8 <= 192, "barrier area");
 
 enum { ST_TIMEOUT_PRODUCER = 1, ST_TIMEOUT_MMA = 2, ST_TIMEOUT_SOFTMAX = 4 };
 
@@ -227,6 +248,12 @@ __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t saddr) {
   return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
          ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
+// K-major operand without swizzle: 8-row x 16-byte core matrices of 128 contiguous bytes; the next
+// 16 bytes along K are 128 bytes further (leading offset), the next 8 rows 1024 bytes (stride offset).
+__device__ __forceinline__ uint64_t kmajor_nosw_desc(uint32_t saddr) {
+  return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)(128 >> 4) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+         ((uint64_t)1 << 46);
+}
 // Instruction descriptor: D format at bit 4, A/B formats at bits 7/10, N>>3 at bit 17, M>>4 at 24.
 constexpr uint32_t IDESC_I8 = (2u << 4) | (1u << 7) | (1u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
 constexpr uint32_t IDESC_F8 = (1u << 4) | (0u << 7) | (0u << 10) | ((128u >> 3) << 17) | ((128u >> 4) << 24);
@@ -260,10 +287,14 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 // ------------------------------------------------------------------------------------------------
 // The kernel.  grid (ceil(N/128), B*H), block 384, two CTAs per SM.
 // ------------------------------------------------------------------------------------------------
-template <bool INT8, bool CAUSAL, typename OutT>
-__global__ void __launch_bounds__(ATT_THREADS, 2)
+template <bool INT8, bool CAUSAL, typename OutT, int NQ>
+__global__ void __launch_bounds__(Shape<NQ>::THREADS, Shape<NQ>::CTAS_PER_SM)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
+  using L = Shape<NQ>;
+  static_assert(NQ == 1 || !CAUSAL, "the two-tile shape serves non-causal calls");
+  constexpr uint32_t OFF_Q = L::OFF_Q, OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_P = L::OFF_P, OFF_SK = L::OFF_SK,
+                     OFF_SV = L::OFF_SV, OFF_BAR = L::OFF_BAR, OFF_MISC = L::OFF_MISC;
   extern __shared__ uint8_t smem_raw[];
   wait_for_predecessor();            // the quantised operands and the status word
   const uint32_t raw_addr = smem_u32(smem_raw);
@@ -275,29 +306,32 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   auto bar = [&](int i) { return bar0 + 8u * (uint32_t)i; };
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int q_tile = CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;   // longest first
+  // first query tile of this CTA (causal: longest first); softmax group g owns tile q_tile0 + g
+  const int q_tile0 = CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : NQ * (int)blockIdx.x;
   const int bh = blockIdx.y;                          // (batch, query head)
   const int bh_kv = (int)((bh / a.Hq) * a.H + (bh % a.Hq) / a.group);   // its (batch, K/V head)
-  const int n_tiles = CAUSAL ? (q_tile + 1) : (int)(a.N_pad / TILE);
+  const int n_tiles = CAUSAL ? (q_tile0 + 1) : (int)(a.N_pad / TILE);
 
   if (tid == 0) {
     mbar_init(bar(BAR_Q), 1);
     for (int s = 0; s < 2; ++s) {
       mbar_init(bar(BAR_KF + s), 1);
-      mbar_init(bar(BAR_KE + s), 1);
+      mbar_init(bar(BAR_KE + s), NQ);                       // every query tile's Q.K^T of the stage is complete
       mbar_init(bar(BAR_VF + s), 1);
-      mbar_init(bar(BAR_VE + s), 1);
+      mbar_init(bar(BAR_VE + s), NQ);
     }
-    mbar_init(bar(BAR_SF), 1);
-    mbar_init(bar(BAR_SFREE), 8);
-    mbar_init(bar(BAR_PF), 8);
-    mbar_init(bar(BAR_PV), 1);
+    for (int g = 0; g < NQ; ++g) {
+      mbar_init(bar(BAR_SF + BAR_PER_TILE * g), 1);
+      mbar_init(bar(BAR_SFREE + BAR_PER_TILE * g), 8);
+      mbar_init(bar(BAR_PF + BAR_PER_TILE * g), 8);
+      mbar_init(bar(BAR_PV + BAR_PER_TILE * g), 1);
+    }
     misc[1] = (*reinterpret_cast<volatile int32_t*>(a.status) != 0) ? 1u : 0u;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
-                 ::"r"(base + OFF_MISC), "r"(TMEM_COLS) : "memory");
+                 ::"r"(base + OFF_MISC), "r"(L::TMEM_COLS) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   tc_fence_before();
@@ -306,22 +340,23 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   const uint32_t tmem = misc[0];
   const bool skip_all = misc[1] != 0u;
 
-  // Registers move from the producer/MMA warpgroup to the two softmax warpgroups:
-  // 384 x 80 at launch = 128 x 32 + 256 x 104 afterwards.  setmaxnreg.inc blocks until the pool
-  // holds the registers it asks for, so the two sides must never add up to more than the launch
-  // allocation (80 per thread: 65536 / (384 x 2 CTAs) rounded down to a multiple of 8).
-  static_assert(128 * REGS_PRODUCER + 256 * REGS_SOFTMAX <= ATT_THREADS * REGS_AT_LAUNCH,
+  // Registers move from the producer/MMA warpgroup to the softmax warpgroups:
+  // 384 x 80 at launch = 128 x 32 + 256 x 104 afterwards (NQ = 2: 640 x 96 = 128 x 32 + 512 x 112).
+  // setmaxnreg.inc blocks until the pool holds the registers it asks for, so the two sides must
+  // never add up to more than the launch allocation.
+  static_assert(128 * L::REGS_PRODUCER + 256 * NQ * L::REGS_SOFTMAX <= L::THREADS * L::REGS_AT_LAUNCH,
                 "setmaxnreg.inc would wait for registers that never become free");
   if (!skip_all) {
     if (warp < 4) {
-      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(REGS_PRODUCER));
+      asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(L::REGS_PRODUCER));
     }
     if (warp == 0) {
       // ------------------------------- TMA producer -------------------------------
       if (lane == 0) {
         prefetch_map(&tm_q); prefetch_map(&tm_k); prefetch_map(&tm_v);
-        mbar_expect_tx(bar(BAR_Q), TILE_BYTES);
-        tma_load_3d(base + OFF_Q, &tm_q, bar(BAR_Q), 0, q_tile * TILE, bh);
+        mbar_expect_tx(bar(BAR_Q), NQ * TILE_BYTES);
+        for (int g = 0; g < NQ; ++g)                          // rows past the last query arrive as zeros
+          tma_load_3d(base + OFF_Q + g * TILE_BYTES, &tm_q, bar(BAR_Q), 0, (q_tile0 + g) * TILE, bh);
         const float* sk_row = a.sk + (size_t)bh_kv * a.N_pad;
         const float* sv_row = a.svp + (size_t)bh_kv * a.N_pad;
         for (int j = 0; j < n_tiles; ++j) {
@@ -339,8 +374,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_3d(base + OFF_V + s * TILE_BYTES, &tm_v, bar(BAR_VF + s), j * TILE, 0, bh_kv);
         }
       }
-    } else if (warp == 1) {
-      // ------------------------------- MMA issuer ---------------------------------
+    } else if (warp == 1 || (NQ == 2 && warp == 2)) {
+      // ------------------------------- MMA issuer (one per query tile) ------------
+      const int g = warp - 1;
+      const int gb = BAR_PER_TILE * g;
       if (lane == 0) {
         constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
         bool ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
@@ -348,29 +385,29 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (j < n_tiles) {
             const int s = j & 1;
             ok = mbar_wait(bar(BAR_KF + s), (uint32_t)(j >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
-            if (ok && j > 0) ok = mbar_wait(bar(BAR_SFREE), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok && j > 0) ok = mbar_wait(bar(BAR_SFREE + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              mma_ss<INT8>(tmem, kmajor_sw128_desc(base + OFF_Q + 32 * k),
+              mma_ss<INT8>(tmem + L::tmem_s(g), kmajor_sw128_desc(base + OFF_Q + g * TILE_BYTES + 32 * k),
                            kmajor_sw128_desc(base + OFF_K + s * TILE_BYTES + 32 * k), IDESC_QK, k > 0);
             tc_commit(bar(BAR_KE + s));
-            tc_commit(bar(BAR_SF));
+            tc_commit(bar(BAR_SF + gb));
           }
           if (j > 0) {
             const int jj = j - 1, s = jj & 1;
             ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(jj >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
-            if (ok) ok = mbar_wait(bar(BAR_PF), (uint32_t)jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok) ok = mbar_wait(bar(BAR_PF + gb), (uint32_t)jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              mma_ss<false>(tmem + TMEM_O, kmajor_sw128_desc(base + OFF_P + 32 * k),
+              mma_ss<false>(tmem + L::tmem_o(g), kmajor_nosw_desc(base + OFF_P + g * TILE_BYTES + 256 * k),
                             kmajor_sw128_desc(base + OFF_V + s * TILE_BYTES + 32 * k), IDESC_F8,
                             (jj > 0 || k > 0) ? 1u : 0u);
             tc_commit(bar(BAR_VE + s));
-            tc_commit(bar(BAR_PV));
+            tc_commit(bar(BAR_PV + gb));
           }
         }
       }
@@ -382,15 +419,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // four columns a thread holds of a 16-column block are four CONSECUTIVE keys 16m+4c..+3:
       // one 16-byte scale load serves both rows, the four e4m3 codes of a row are one 32-bit word of
       // the P tile, and a row's maximum is two shuffles among the four threads that share it.
-      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(REGS_SOFTMAX));
+      asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(L::REGS_SOFTMAX));
+      const int g = (NQ == 1) ? 0 : (warp - 4) >> 3;        // which query tile of the CTA
+      const int gb = BAR_PER_TILE * g;
+      const int q_tile = q_tile0 + g;
       const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
-      const int sub = (warp - 4) >> 2;                      // which 16 lanes of the quarter
+      const int sub = ((warp - 4) >> 2) & 1;                // which 16 lanes of the quarter
       const int r0 = lane >> 2, c = lane & 3;
       const int lane_base = 32 * quarter + 16 * sub;
       const int rowA = lane_base + r0, rowB = rowA + 8;     // this thread's two query rows of the tile
       const long long q_rowA = (long long)q_tile * TILE + rowA, q_rowB = q_rowA + 8;
-      const uint32_t t_s = tmem + ((uint32_t)lane_base << 16);
-      const uint32_t t_o = t_s + TMEM_O;
+      const uint32_t t_s = tmem + ((uint32_t)lane_base << 16) + L::tmem_s(g);
+      const uint32_t t_o = tmem + ((uint32_t)lane_base << 16) + L::tmem_o(g);
       // c_q = f32(f32(sm_scale * log2e) * sq); rows past N get 1 (their scores are all zero)
       const float sl2 = __fmul_rn(a.sm_scale, LOG2E_F);
       const float cqA = (q_rowA < a.Nq) ? __fmul_rn(sl2, __ldg(a.sq + (size_t)bh * a.Nq + q_rowA)) : 1.f;
@@ -398,14 +438,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const float2 cqA2 = make_float2(cqA, cqA), cqB2 = make_float2(cqB, cqB);
       float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
       bool ok = true;
-      // P tile: row r at r*128, 16-byte chunk m at (16m) ^ ((r & 7) << 4); rowA & 7 == rowB & 7 == r0
-      const uint32_t swz = (uint32_t)r0 << 4;
-      const uint32_t pA = base + OFF_P + (uint32_t)rowA * 128u + 4u * (uint32_t)c, pB = pA + 8u * 128u;
+      // P tile: 16 keys of row r (chunk m) at (r / 8) * 1024 + m * 128 + (r % 8) * 16, so that the
+      // eight stores of a row differ by a constant and a warp's store covers 128 contiguous bytes
+      const uint32_t pA = base + OFF_P + (uint32_t)g * TILE_BYTES + (uint32_t)lane_base * 128u + 16u * (uint32_t)r0 +
+                          4u * (uint32_t)c;
+      const uint32_t pB = pA + 8u * 128u;
       const uint32_t sk_c = base + OFF_SK + 16u * (uint32_t)c;   // scales of keys 16m+4c..+3 at + 64m
 
       for (int j = 0; j < n_tiles; ++j) {
         // S(j) complete implies the K stage, and with it this tile's scale rows, has landed
-        ok = mbar_wait(bar(BAR_SF), (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        ok = mbar_wait(bar(BAR_SF + gb), (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
         tc_fence_after();
@@ -414,7 +456,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         tmem_ld_wait();
         tc_fence_before();
         __syncwarp();
-        mbar_arrive_lane0(bar(BAR_SFREE), lane);
+        mbar_arrive_lane0(bar(BAR_SFREE + gb), lane);
         if (a.dbg != nullptr && j == a.dbg_tile) {
           uint32_t* dA = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + rowA) * TILE + 4 * c;
           uint32_t* dB = dA + 8 * TILE;
@@ -496,7 +538,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float alphaA = ex2(cqA * (mA - mA_use)), alphaB = ex2(cqB * (mB - mB_use));
 
         if (j > 0) {
-          ok = mbar_wait(bar(BAR_PV), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+          ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
           tc_fence_after();
@@ -520,7 +562,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
             psA = __fadd2_rn(psA, __fadd2_rn(p01, p23));
             const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
-            sts32u(pA + ((16u * (uint32_t)m) ^ swz), e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
+            sts32u(pA + 128u * (uint32_t)m, e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
           }
           {
             const float2 t0 = __ffma2_rn(uB[2 * m + 0], cqB2, nmB2);
@@ -529,7 +571,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
             psB = __fadd2_rn(psB, __fadd2_rn(p01, p23));
             const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
-            sts32u(pB + ((16u * (uint32_t)m) ^ swz), e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
+            sts32u(pB + 128u * (uint32_t)m, e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
           }
         }
         lA = lA * alphaA + (psA.x + psA.y);                 // this thread's quarter of the row sum
@@ -552,12 +594,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
-        mbar_arrive_lane0(bar(BAR_PF), lane);
+        mbar_arrive_lane0(bar(BAR_PF + gb), lane);
       }
 
       // ------------------------------- epilogue -----------------------------------
       if (ok) {
-        ok = mbar_wait(bar(BAR_PV), (uint32_t)(n_tiles - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+        ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(n_tiles - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
       }
       if (ok) {
@@ -616,7 +658,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   }
   if (warp == 1) {
     tc_fence_after();
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(L::TMEM_COLS) : "memory");
   }
 }
 
@@ -657,12 +699,15 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t r
 
 static uint32_t* g_dbg_ptr = nullptr;
 static int g_dbg_tile = 0;
+static int g_force_tiles_per_cta = 0;
 void set_score_dump(void* ptr, int tile) { g_dbg_ptr = reinterpret_cast<uint32_t*>(ptr); g_dbg_tile = tile; }
+void set_tiles_per_cta(int n) { g_force_tiles_per_cta = (n == 1 || n == 2) ? n : 0; }
 
-template <bool INT8, bool CAUSAL, typename OutT>
+template <bool INT8, bool CAUSAL, typename OutT, int NQ>
 static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                                const AttnKArgs& ka, dim3 grid, cudaStream_t st) {
-  auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT>;
+  auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT, NQ>;
+  using L = Shape<NQ>;
   // the opt-in to more than 48 KB of dynamic shared memory is per device and per instantiation;
   // it is made once (short calls are dominated by host-side work)
   static bool opted_in[64] = {false};
@@ -670,17 +715,17 @@ static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, con
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
   if (dev < 0 || dev >= 64 || !opted_in[dev]) {
-    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)L::SMEM_BYTES);
     if (e != cudaSuccess) return e;
     // The register hand-over inside the kernel assumes the allocation the compiler reported; a
     // build that came out with fewer registers per thread would leave setmaxnreg.inc waiting.
     cudaFuncAttributes attr;
     e = cudaFuncGetAttributes(&attr, kern);
     if (e != cudaSuccess) return e;
-    if (attr.numRegs * ATT_THREADS < 128 * REGS_PRODUCER + 256 * REGS_SOFTMAX) return cudaErrorLaunchOutOfResources;
+    if (attr.numRegs * L::THREADS < 128 * L::REGS_PRODUCER + 256 * NQ * L::REGS_SOFTMAX) return cudaErrorLaunchOutOfResources;
     if (dev >= 0 && dev < 64) opted_in[dev] = true;
   }
-  return launch_after_predecessor(kern, grid, dim3(ATT_THREADS), SMEM_BYTES, st, mq, mk, mv, ka);
+  return launch_after_predecessor(kern, grid, dim3(L::THREADS), L::SMEM_BYTES, st, mq, mk, mv, ka);
 }
 
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why) {
@@ -700,18 +745,36 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
   ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;
-  dim3 grid((unsigned)((p.Nq + TILE - 1) / TILE), (unsigned)bhq);
+  // Two query tiles per CTA when the call is non-causal and has at least one such CTA for every SM;
+  // smaller calls keep the one-tile shape, which spreads over more CTAs.  (The score dump indexes by
+  // one-tile CTAs.)
+  const unsigned q_tiles = (unsigned)((p.Nq + TILE - 1) / TILE);
+  static int sm_count[64] = {0};                          // per device, asked once
+  int sms = 148, dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64) {
+    if (sm_count[dev] == 0 &&
+        cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev) != cudaSuccess)
+      sm_count[dev] = 148;
+    sms = sm_count[dev];
+  }
+  bool two = !p.causal && q_tiles >= 2 && g_dbg_ptr == nullptr && (uint64_t)((q_tiles + 1) / 2) * bhq >= (uint64_t)sms;
+  if (g_force_tiles_per_cta != 0 && !p.causal && g_dbg_ptr == nullptr) two = (g_force_tiles_per_cta == 2);
+  dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
   cudaError_t e;
   switch (key) {
-    case 7: e = launch_inst<true, true, __half>(mq, mk, mv, ka, grid, st); break;
-    case 6: e = launch_inst<true, true, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
-    case 5: e = launch_inst<true, false, __half>(mq, mk, mv, ka, grid, st); break;
-    case 4: e = launch_inst<true, false, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
-    case 3: e = launch_inst<false, true, __half>(mq, mk, mv, ka, grid, st); break;
-    case 2: e = launch_inst<false, true, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
-    case 1: e = launch_inst<false, false, __half>(mq, mk, mv, ka, grid, st); break;
-    default: e = launch_inst<false, false, __nv_bfloat16>(mq, mk, mv, ka, grid, st); break;
+    case 7: e = launch_inst<true, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
+    case 6: e = launch_inst<true, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
+    case 5: e = two ? launch_inst<true, false, __half, 2>(mq, mk, mv, ka, grid, st)
+                    : launch_inst<true, false, __half, 1>(mq, mk, mv, ka, grid, st); break;
+    case 4: e = two ? launch_inst<true, false, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
+                    : launch_inst<true, false, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
+    case 3: e = launch_inst<false, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
+    case 2: e = launch_inst<false, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
+    case 1: e = two ? launch_inst<false, false, __half, 2>(mq, mk, mv, ka, grid, st)
+                    : launch_inst<false, false, __half, 1>(mq, mk, mv, ka, grid, st); break;
+    default: e = two ? launch_inst<false, false, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
+                     : launch_inst<false, false, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
   }
   if (e != cudaSuccess && why) *why = "attention kernel launch failed";
   return e;

@@ -298,6 +298,8 @@ int sage_attn_fwd_ex(const void* q8, const float* sq, const void* k8, const floa
 
 void sage_debug_score_dump(void* ptr, int key_tile) { sage::set_score_dump(ptr, key_tile); }
 
+void sage_debug_tiles_per_cta(int n) { sage::set_tiles_per_cta(n); }
+
 size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N) {
   if (B < 1 || H < 1 || N < 1) return 0;
   const Dims d = {B, H, H, N, N, sage::HD};

@@ -1,0 +1,88 @@
+"""The attention kernel's two shapes -- one or two 128-query tiles per CTA -- must agree bit for bit:
+both compute a row with the same instructions in the same order, only the scheduling differs.  The
+automatic choice takes two tiles only for large non-causal calls, so the small cases here force
+each shape through `sage_debug_tiles_per_cta` and compare; the forced two-tile result is also held
+against the oracle."""
+import pytest
+import torch
+
+from oracle import ref_numerics as R
+from sageattention import _native
+from sageattention import b200_backend as be
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def force_shape():
+    lib = _native.load()
+    yield lib.sage_debug_tiles_per_cta
+    lib.sage_debug_tiles_per_cta(0)
+
+
+def _inputs(b, hq, hkv, nq, nk, d, dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(b, hq, nq, d, generator=g).to(dtype)
+    k = (torch.randn(b, hkv, nk, d, generator=g) + 0.5 * torch.randn(1, hkv, 1, d, generator=g)).to(dtype)
+    v = torch.randn(b, hkv, nk, d, generator=g).to(dtype)
+    return q, k, v
+
+
+CASES = [
+    # b, hq, hkv, nq, nk, d, dtype, int8, smooth_v
+    (1, 4, 4, 300, 300, 128, torch.float16, True, False),     # 3 query tiles: the last CTA's second tile is empty
+    (2, 8, 2, 513, 1000, 128, torch.bfloat16, True, False),   # grouped heads, ragged last tile on both sides
+    (1, 2, 2, 256, 129, 64, torch.float16, True, False),      # exactly two tiles, head_dim 64
+    (1, 3, 3, 1024, 1024, 128, torch.bfloat16, False, False), # e4m3 Q/K codes
+    (1, 4, 2, 700, 515, 128, torch.float16, True, True),      # smooth_v
+    (3, 1, 1, 129, 4096, 128, torch.float16, True, False),    # one row in the second tile, many key tiles
+]
+
+
+@pytest.mark.parametrize("b,hq,hkv,nq,nk,d,dtype,int8,smooth_v", CASES)
+def test_both_shapes_agree_bit_for_bit(force_shape, b, hq, hkv, nq, nk, d, dtype, int8, smooth_v):
+    q, k, v = (t.cuda() for t in _inputs(b, hq, hkv, nq, nk, d, dtype, nq + nk))
+    results = []
+    for n in (1, 2):
+        force_shape(n)
+        out, lse = be.sage_call(q, k, v, is_causal=False, int8=int8, return_lse=True, smooth_v=smooth_v)
+        torch.cuda.synchronize()
+        assert be.last_status(out, b, hq, nq, hkv, nk) == 0
+        results.append((out.clone(), lse.clone()))
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+def test_two_tile_shape_against_the_oracle(force_shape, dtype):
+    q, k, v = _inputs(2, 3, 3, 640, 640, 128, dtype, 7)
+    force_shape(2)
+    out = be.sage_call(q.cuda(), k.cuda(), v.cuda(), is_causal=False)
+    torch.cuda.synchronize()
+    assert be.last_status(out, 2, 3, 640) == 0
+    want = R.sageattn_oracle(q, k, v, is_causal=False, tile=128)
+    # same tolerances as the one-tile parity tests: same quantised operands, fp32 order differs
+    assert R.cosine(out.cpu(), want) >= 0.9999
+    assert R.rel_l1(out.cpu(), want) <= 5e-3
+
+
+def test_forcing_a_shape_leaves_causal_calls_alone(force_shape):
+    q, k, v = (t.cuda() for t in _inputs(1, 2, 2, 400, 400, 128, torch.float16, 3))
+    ref = be.sage_call(q, k, v, is_causal=True).clone()
+    force_shape(2)
+    out = be.sage_call(q, k, v, is_causal=True)
+    torch.cuda.synchronize()
+    assert be.last_status(out, 1, 2, 400) == 0
+    assert torch.equal(out, ref)
+
+
+def test_automatic_choice_serves_a_call_large_enough_for_two_tiles():
+    # 8 heads x 40 query tiles: 160 two-tile CTAs >= the SM count, so this runs the two-tile shape
+    # without being forced; parity as everywhere else
+    q, k, v = _inputs(1, 8, 8, 5120, 512, 128, torch.float16, 11)
+    out = be.sage_call(q.cuda(), k.cuda(), v.cuda(), is_causal=False)
+    torch.cuda.synchronize()
+    assert be.last_status(out, 1, 8, 5120, 8, 512) == 0
+    want = R.sageattn_oracle(q, k, v, is_causal=False, tile=128)
+    assert R.cosine(out.cpu(), want) >= 0.9999
+    assert R.rel_l1(out.cpu(), want) <= 5e-3
