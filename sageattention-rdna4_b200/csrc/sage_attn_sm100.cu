@@ -3,11 +3,11 @@
 // A query tile is 128 queries of one (batch, head); it streams 128-key tiles.  The kernel comes in
 // two shapes (template parameter NQ, query tiles per CTA):
 //   NQ = 1   one query tile per CTA, 384 threads, two CTAs per SM, so that one CTA's softmax
-//            overlaps the other's matrix products.  Causal calls and calls too small to give every
-//            SM a two-tile CTA.
+//            overlaps the other's matrix products.  Calls too small to give every SM a two-tile CTA.
 //   NQ = 2   two neighbouring query tiles of a head per CTA, 640 threads, one CTA per SM: each K
 //            and V^T tile is loaded once for both, each query tile has its own softmax warps,
-//            TMEM columns, P tile and MMA-issuing thread.  Non-causal calls.
+//            TMEM columns, P tile and MMA-issuing thread.  (Causal: the second tile visits one
+//            key tile more than the first.)
 // Both shapes compute every row with the same instructions in the same order.  Roles inside a CTA:
 //   warp 0     TMA producer: the Q tile(s) once, then a 2-deep ring of K tiles (each carrying that
 //              tile's 128 K scales and 128 staged V factors into a 4-slot ring) and a 2-deep ring
@@ -292,7 +292,6 @@ __global__ void __launch_bounds__(Shape<NQ>::THREADS, Shape<NQ>::CTAS_PER_SM)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
   using L = Shape<NQ>;
-  static_assert(NQ == 1 || !CAUSAL, "the two-tile shape serves non-causal calls");
   constexpr uint32_t OFF_Q = L::OFF_Q, OFF_K = L::OFF_K, OFF_V = L::OFF_V, OFF_P = L::OFF_P, OFF_SK = L::OFF_SK,
                      OFF_SV = L::OFF_SV, OFF_BAR = L::OFF_BAR, OFF_MISC = L::OFF_MISC;
   extern __shared__ uint8_t smem_raw[];
@@ -307,10 +306,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
 
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   // first query tile of this CTA (causal: longest first); softmax group g owns tile q_tile0 + g
-  const int q_tile0 = CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : NQ * (int)blockIdx.x;
+  const int q_tile0 = NQ * (CAUSAL ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x);
   const int bh = blockIdx.y;                          // (batch, query head)
   const int bh_kv = (int)((bh / a.Hq) * a.H + (bh % a.Hq) / a.group);   // its (batch, K/V head)
-  const int n_tiles = CAUSAL ? (q_tile0 + 1) : (int)(a.N_pad / TILE);
+  // Key tiles query tile g visits: all of them, or when causal those up to its diagonal (a causal
+  // call has as many key tiles as query tiles; the second tile of the last CTA may not exist, it
+  // then repeats the first one's range and stores nothing).  The producer loads the longer range.
+  const int key_tiles = (int)(a.N_pad / TILE);
+  auto tiles_of = [&](int g) { return CAUSAL ? min(q_tile0 + g + 1, key_tiles) : key_tiles; };
+  const int n_load = tiles_of(NQ - 1);
 
   if (tid == 0) {
     mbar_init(bar(BAR_Q), 1);
@@ -359,7 +363,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_3d(base + OFF_Q + g * TILE_BYTES, &tm_q, bar(BAR_Q), 0, (q_tile0 + g) * TILE, bh);
         const float* sk_row = a.sk + (size_t)bh_kv * a.N_pad;
         const float* sv_row = a.svp + (size_t)bh_kv * a.N_pad;
-        for (int j = 0; j < n_tiles; ++j) {
+        for (int j = 0; j < n_load; ++j) {
           const int s = j & 1;
           const uint32_t par = ((uint32_t)(j >> 1) & 1u) ^ 1u;
           if (!mbar_wait(bar(BAR_KE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
@@ -378,6 +382,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       // ------------------------------- MMA issuer (one per query tile) ------------
       const int g = warp - 1;
       const int gb = BAR_PER_TILE * g;
+      const int n_tiles = tiles_of(g);
       if (lane == 0) {
         constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
         bool ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
@@ -423,6 +428,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int g = (NQ == 1) ? 0 : (warp - 4) >> 3;        // which query tile of the CTA
       const int gb = BAR_PER_TILE * g;
       const int q_tile = q_tile0 + g;
+      const int n_tiles = tiles_of(g);
       const int quarter = warp & 3;                         // TMEM lane quarter this warp may touch
       const int sub = ((warp - 4) >> 2) & 1;                // which 16 lanes of the quarter
       const int r0 = lane >> 2, c = lane & 3;
@@ -745,9 +751,8 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
   ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;
-  // Two query tiles per CTA when the call is non-causal and has at least one such CTA for every SM;
-  // smaller calls keep the one-tile shape, which spreads over more CTAs.  (The score dump indexes by
-  // one-tile CTAs.)
+  // Two query tiles per CTA when the call has at least one such CTA for every SM; smaller calls
+  // keep the one-tile shape, which spreads over more CTAs.  (The score dump indexes by one-tile CTAs.)
   const unsigned q_tiles = (unsigned)((p.Nq + TILE - 1) / TILE);
   static int sm_count[64] = {0};                          // per device, asked once
   int sms = 148, dev = 0;
@@ -757,20 +762,24 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
       sm_count[dev] = 148;
     sms = sm_count[dev];
   }
-  bool two = !p.causal && q_tiles >= 2 && g_dbg_ptr == nullptr && (uint64_t)((q_tiles + 1) / 2) * bhq >= (uint64_t)sms;
-  if (g_force_tiles_per_cta != 0 && !p.causal && g_dbg_ptr == nullptr) two = (g_force_tiles_per_cta == 2);
+  bool two = q_tiles >= 2 && g_dbg_ptr == nullptr && (uint64_t)((q_tiles + 1) / 2) * bhq >= (uint64_t)sms;
+  if (g_force_tiles_per_cta != 0 && g_dbg_ptr == nullptr) two = (g_force_tiles_per_cta == 2);
   dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
   cudaError_t e;
   switch (key) {
-    case 7: e = launch_inst<true, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
-    case 6: e = launch_inst<true, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
+    case 7: e = two ? launch_inst<true, true, __half, 2>(mq, mk, mv, ka, grid, st)
+                    : launch_inst<true, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
+    case 6: e = two ? launch_inst<true, true, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
+                    : launch_inst<true, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
     case 5: e = two ? launch_inst<true, false, __half, 2>(mq, mk, mv, ka, grid, st)
                     : launch_inst<true, false, __half, 1>(mq, mk, mv, ka, grid, st); break;
     case 4: e = two ? launch_inst<true, false, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
                     : launch_inst<true, false, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
-    case 3: e = launch_inst<false, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
-    case 2: e = launch_inst<false, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
+    case 3: e = two ? launch_inst<false, true, __half, 2>(mq, mk, mv, ka, grid, st)
+                    : launch_inst<false, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
+    case 2: e = two ? launch_inst<false, true, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
+                    : launch_inst<false, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
     case 1: e = two ? launch_inst<false, false, __half, 2>(mq, mk, mv, ka, grid, st)
                     : launch_inst<false, false, __half, 1>(mq, mk, mv, ka, grid, st); break;
     default: e = two ? launch_inst<false, false, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)

@@ -1,6 +1,6 @@
 """The attention kernel's two shapes -- one or two 128-query tiles per CTA -- must agree bit for bit:
 both compute a row with the same instructions in the same order, only the scheduling differs.  The
-automatic choice takes two tiles only for large non-causal calls, so the small cases here force
+automatic choice takes two tiles only for large calls, so the small cases here force
 each shape through `sage_debug_tiles_per_cta` and compare; the forced two-tile result is also held
 against the oracle."""
 import pytest
@@ -66,14 +66,35 @@ def test_two_tile_shape_against_the_oracle(force_shape, dtype):
     assert R.rel_l1(out.cpu(), want) <= 5e-3
 
 
-def test_forcing_a_shape_leaves_causal_calls_alone(force_shape):
-    q, k, v = (t.cuda() for t in _inputs(1, 2, 2, 400, 400, 128, torch.float16, 3))
-    ref = be.sage_call(q, k, v, is_causal=True).clone()
+@pytest.mark.parametrize("b,hq,hkv,n,d,dtype,int8", [
+    (1, 2, 2, 400, 128, torch.float16, True),      # 4 query tiles, ragged diagonal tile
+    (2, 6, 3, 641, 128, torch.bfloat16, True),     # 6 tiles, one row in the last; grouped heads
+    (1, 3, 3, 300, 64, torch.float16, True),       # 3 tiles: the longest CTA's second tile does not exist
+    (1, 2, 2, 1280, 128, torch.bfloat16, False),   # e4m3 Q/K codes
+    (1, 1, 1, 129, 128, torch.float16, True),      # 2 tiles, one row in the second
+])
+def test_both_shapes_agree_bit_for_bit_when_causal(force_shape, b, hq, hkv, n, d, dtype, int8):
+    q, k, v = (t.cuda() for t in _inputs(b, hq, hkv, n, n, d, dtype, n))
+    results = []
+    for shape in (1, 2):
+        force_shape(shape)
+        out, lse = be.sage_call(q, k, v, is_causal=True, int8=int8, return_lse=True)
+        torch.cuda.synchronize()
+        assert be.last_status(out, b, hq, n, hkv, n) == 0
+        results.append((out.clone(), lse.clone()))
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
+
+
+def test_two_tile_shape_against_the_oracle_when_causal(force_shape):
+    q, k, v = _inputs(1, 3, 3, 700, 700, 128, torch.float16, 5)
     force_shape(2)
-    out = be.sage_call(q, k, v, is_causal=True)
+    out = be.sage_call(q.cuda(), k.cuda(), v.cuda(), is_causal=True)
     torch.cuda.synchronize()
-    assert be.last_status(out, 1, 2, 400) == 0
-    assert torch.equal(out, ref)
+    assert be.last_status(out, 1, 3, 700) == 0
+    want = R.sageattn_oracle(q, k, v, is_causal=True, tile=128)
+    assert R.cosine(out.cpu(), want) >= 0.9999
+    assert R.rel_l1(out.cpu(), want) <= 5e-3
 
 
 def test_automatic_choice_serves_a_call_large_enough_for_two_tiles():
