@@ -285,7 +285,8 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 }
 
 // ------------------------------------------------------------------------------------------------
-// The kernel.  grid (ceil(N/128), B*H), block 384, two CTAs per SM.
+// The kernel.  NQ = 1: grid (ceil(Nq/128), B*Hq), block 384, two CTAs per SM; NQ = 2: grid
+// (ceil(Nq/256), B*Hq), block 640, one CTA per SM.
 // ------------------------------------------------------------------------------------------------
 template <bool INT8, bool CAUSAL, typename OutT, int NQ>
 __global__ void __launch_bounds__(Shape<NQ>::THREADS, Shape<NQ>::CTAS_PER_SM)
