@@ -107,3 +107,32 @@ def test_automatic_choice_serves_a_call_large_enough_for_two_tiles():
     want = R.sageattn_oracle(q, k, v, is_causal=False, tile=128)
     assert R.cosine(out.cpu(), want) >= 0.9999
     assert R.rel_l1(out.cpu(), want) <= 5e-3
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_shapes_agree_on_random_calls(force_shape, seed):
+    """Seeded random call shapes (lengths, head counts, grouping, head_dim, dtype, causal, code type,
+    smooth_v): the two kernel shapes must return the same bits."""
+    g = torch.Generator().manual_seed(1000 + seed)
+    ri = lambda lo, hi: int(torch.randint(lo, hi + 1, (1,), generator=g).item())
+    causal = bool(ri(0, 1))
+    hkv = ri(1, 3)
+    hq = hkv * ri(1, 3)
+    nq = ri(129, 1100)
+    nk = nq if causal else ri(1, 1100)
+    d = (128, 128, 64, 96, 40)[ri(0, 4)]
+    dtype = (torch.float16, torch.bfloat16)[ri(0, 1)]
+    int8 = bool(ri(0, 3))
+    smooth_v = bool(ri(0, 1))
+    b = ri(1, 2)
+    q, k, v = (t.cuda() for t in _inputs(b, hq, hkv, nq, nk, d, dtype, seed))
+    results = []
+    for shape in (1, 2):
+        force_shape(shape)
+        out, lse = be.sage_call(q, k, v, is_causal=causal, int8=int8, return_lse=True, smooth_v=smooth_v)
+        torch.cuda.synchronize()
+        assert be.last_status(out, b, hq, nq, hkv, nk) == 0
+        results.append((out.clone(), lse.clone()))
+    assert torch.isfinite(results[0][0].float()).all()
+    assert torch.equal(results[0][0], results[1][0])
+    assert torch.equal(results[0][1], results[1][1])
