@@ -60,8 +60,12 @@ template <int NQ> struct Shape {
   static constexpr uint32_t OFF_Q = 0;
   static constexpr uint32_t OFF_K = OFF_Q + NQ * TILE_BYTES;    // 2 stages
   static constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;     // 2 stages
-  static constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;     // one P tile per query tile
-  static constexpr uint32_t OFF_SK = OFF_P + NQ * TILE_BYTES;   // 4-slot ring of K scales (arrive with the K tile)
+  // P tiles per query tile.  With two, the softmax warps write P(j) without waiting for the product
+  // that reads P(j-1), and wait for it only where they need the output accumulator; two one-tile
+  // CTAs would not fit an SM with the second buffer.
+  static constexpr int P_BUFS = (NQ == 2) ? 2 : 1;
+  static constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;
+  static constexpr uint32_t OFF_SK = OFF_P + NQ * P_BUFS * TILE_BYTES;   // 4-slot ring of K scales (arrive with the K tile)
   static constexpr uint32_t OFF_SV = OFF_SK + 4 * VEC_BYTES;    // 4-slot ring of staged V factors (same barrier)
   static constexpr uint32_t OFF_BAR = OFF_SV + 4 * VEC_BYTES;
   static constexpr uint32_t OFF_MISC = OFF_BAR + 192;
@@ -409,7 +413,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_fence_after();
 #pragma unroll
             for (int k = 0; k < 4; ++k)
-              mma_ss<false>(tmem + L::tmem_o(g), kmajor_nosw_desc(base + OFF_P + g * TILE_BYTES + 256 * k),
+              mma_ss<false>(tmem + L::tmem_o(g),
+                            kmajor_nosw_desc(base + OFF_P + (g * L::P_BUFS + (jj & (L::P_BUFS - 1))) * TILE_BYTES + 256 * k),
                             kmajor_sw128_desc(base + OFF_V + s * TILE_BYTES + 32 * k), IDESC_F8,
                             (jj > 0 || k > 0) ? 1u : 0u);
             tc_commit(bar(BAR_VE + s));
@@ -447,9 +452,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       bool ok = true;
       // P tile: 16 keys of row r (chunk m) at (r / 8) * 1024 + m * 128 + (r % 8) * 16, so that the
       // eight stores of a row differ by a constant and a warp's store covers 128 contiguous bytes
-      const uint32_t pA = base + OFF_P + (uint32_t)g * TILE_BYTES + (uint32_t)lane_base * 128u + 16u * (uint32_t)r0 +
-                          4u * (uint32_t)c;
-      const uint32_t pB = pA + 8u * 128u;
+      const uint32_t p0 = base + OFF_P + (uint32_t)(g * L::P_BUFS) * TILE_BYTES + (uint32_t)lane_base * 128u +
+                          16u * (uint32_t)r0 + 4u * (uint32_t)c;
       const uint32_t sk_c = base + OFF_SK + 16u * (uint32_t)c;   // scales of keys 16m+4c..+3 at + 64m
 
       for (int j = 0; j < n_tiles; ++j) {
@@ -544,7 +548,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float mB_use = (mB_new == -INFINITY) ? 0.f : mB_new;
         const float alphaA = ex2(cqA * (mA - mA_use)), alphaB = ex2(cqB * (mB - mB_use));
 
-        if (j > 0) {
+        // P.V(j-1) must be complete before the accumulator is rescaled and, with a single P tile,
+        // before P(j) overwrites P(j-1).  With two P tiles the wait moves behind the exponentials,
+        // where it no longer stalls: P(j) goes to the tile P.V(j-2) read, and that product was
+        // waited for in the previous iteration.
+        if (L::P_BUFS == 1 && j > 0) {
           ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
@@ -555,6 +563,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const bool rescale = (j > 0) && __any_sync(0xffffffffu, (mA_new > mA) || (mB_new > mB));
         mA = mA_new; mB = mB_new;
 
+        const uint32_t pA = p0 + (uint32_t)(j & (L::P_BUFS - 1)) * TILE_BYTES, pB = pA + 8u * 128u;
         const float nmA = -(cqA * mA_use), nmB = -(cqB * mB_use);
         const float2 nmA2 = make_float2(nmA, nmA), nmB2 = make_float2(nmB, nmB);
         float2 psA = make_float2(0.f, 0.f), psB = make_float2(0.f, 0.f);
@@ -583,6 +592,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         lA = lA * alphaA + (psA.x + psA.y);                 // this thread's quarter of the row sum
         lB = lB * alphaB + (psB.x + psB.y);
+        if (L::P_BUFS == 2 && j > 0) {
+          ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+          ok = __all_sync(0xffffffffu, ok);
+          if (!ok) break;
+          tc_fence_after();
+        }
         if (rescale) {
           const float2 aA2 = make_float2(alphaA, alphaA), aB2 = make_float2(alphaB, alphaB);
           uint32_t o[64];
