@@ -767,8 +767,13 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
   ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;
-  // Two query tiles per CTA when the call has at least one such CTA for every SM; smaller calls
-  // keep the one-tile shape, which spreads over more CTAs.  (The score dump indexes by one-tile CTAs.)
+  // Which shape.  A two-tile CTA does the work of two one-tile CTAs in about 0.92 of the time the
+  // two take side by side on an SM, but it is handed out in units twice as large.  Non-causal CTAs
+  // all take the same time, so the count of rounds decides: one-tile CTAs go round in half-SM
+  // units (ceil(S / SMs) / 2 rounds for S CTAs), two-tile CTAs in whole ones (ceil(P / SMs) rounds
+  // for P = about S / 2); a call that is resident at once either way is faster with two tiles.
+  // Causal CTAs differ in length and even out by themselves; they take two tiles once there is
+  // such a CTA for every SM.  (The score dump indexes by one-tile CTAs.)
   const unsigned q_tiles = (unsigned)((p.Nq + TILE - 1) / TILE);
   static int sm_count[64] = {0};                          // per device, asked once
   int sms = 148, dev = 0;
@@ -778,7 +783,19 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
       sm_count[dev] = 148;
     sms = sm_count[dev];
   }
-  bool two = q_tiles >= 2 && g_dbg_ptr == nullptr && (uint64_t)((q_tiles + 1) / 2) * bhq >= (uint64_t)sms;
+  const uint64_t n_one = (uint64_t)q_tiles * bhq, n_two = (uint64_t)((q_tiles + 1) / 2) * bhq;
+  bool two = false;
+  if (q_tiles >= 2 && g_dbg_ptr == nullptr) {
+    if (p.causal) {
+      two = n_two >= (uint64_t)sms;
+    } else if (n_one <= 2 * (uint64_t)sms) {
+      two = true;
+    } else {
+      const double rounds_one = 0.5 * (double)((n_one + sms - 1) / sms);
+      const double rounds_two = 0.92 * (double)((n_two + sms - 1) / sms);
+      two = rounds_two <= rounds_one;
+    }
+  }
   if (g_force_tiles_per_cta != 0 && g_dbg_ptr == nullptr) two = (g_force_tiles_per_cta == 2);
   dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
