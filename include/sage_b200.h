@@ -133,8 +133,8 @@ int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* 
 void sage_debug_score_dump(void* ptr, int key_tile);
 
 /* Debugging aid (process-global, not thread-safe): the attention kernel has two shapes, one or two
- * 128-query tiles per CTA, and picks two for calls that are large enough to give every SM such a
- * CTA.  n = 1 or 2 forces that shape for later launches, anything else restores the automatic
+ * 128-query tiles per CTA, and picks the one it expects to finish sooner for the call's size.
+ * n = 1 or 2 forces that shape for later launches, anything else restores the automatic
  * choice.  Both shapes give bit-identical results. */
 void sage_debug_tiles_per_cta(int n);
 

@@ -3,11 +3,12 @@
 // A query tile is 128 queries of one (batch, head); it streams 128-key tiles.  The kernel comes in
 // two shapes (template parameter NQ, query tiles per CTA):
 //   NQ = 1   one query tile per CTA, 384 threads, two CTAs per SM, so that one CTA's softmax
-//            overlaps the other's matrix products.  Calls too small to give every SM a two-tile CTA.
+//            overlaps the other's matrix products.  Calls whose two-tile grid would end in a
+//            nearly empty round (see launch_attention).
 //   NQ = 2   two neighbouring query tiles of a head per CTA, 640 threads, one CTA per SM: each K
 //            and V^T tile is loaded once for both, each query tile has its own softmax warps,
-//            TMEM columns, P tile and MMA-issuing thread.  (Causal: the second tile visits one
-//            key tile more than the first.)
+//            TMEM columns, pair of P tiles and MMA-issuing thread.  (Causal: the second tile
+//            visits one key tile more than the first.)
 // Both shapes compute every row with the same instructions in the same order.  Roles inside a CTA:
 //   warp 0     TMA producer: the Q tile(s) once, then a 2-deep ring of K tiles (each carrying that
 //              tile's 128 K scales and 128 staged V factors into a 4-slot ring) and a 2-deep ring
