@@ -138,6 +138,10 @@ void sage_debug_score_dump(void* ptr, int key_tile);
  * choice.  Both shapes give bit-identical results. */
 void sage_debug_tiles_per_cta(int n);
 
+/* The shape the attention kernel takes, left to itself, for B x Hq heads of Nq queries on a device
+ * with sm_count SMs: 1 or 2 query tiles per CTA (0 for bad arguments).  Host arithmetic only. */
+int sage_attention_tiles_per_cta(int64_t B, int64_t Hq, int64_t Nq, int causal, int sm_count);
+
 /* Bytes of workspace `sage_attention` needs for one call (all intermediates + ctrl + status). */
 size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N);
 

@@ -751,6 +751,24 @@ static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, con
   return launch_after_predecessor(kern, grid, dim3(L::THREADS), L::SMEM_BYTES, st, mq, mk, mv, ka);
 }
 
+// Which shape: query tiles per CTA for a call of `q_tiles` x `bhq` query tiles on `sms` SMs.
+// A two-tile CTA does the work of two one-tile CTAs in about 0.92 of the time the two take side
+// by side on an SM, but it is handed out in units twice as large.  Non-causal CTAs
+// all take the same time, so the count of rounds decides: one-tile CTAs go round in half-SM
+// units (ceil(S / SMs) / 2 rounds for S CTAs), two-tile CTAs in whole ones (ceil(P / SMs) rounds
+// for P = about S / 2); a call that is resident at once either way is faster with two tiles.
+// Causal CTAs differ in length and even out by themselves; they take two tiles once there is
+// such a CTA for every SM.
+int choose_tiles_per_cta(int64_t q_tiles, int64_t bhq, bool causal, int sms) {
+  if (q_tiles < 2 || bhq < 1 || sms < 1) return 1;
+  const uint64_t n_one = (uint64_t)q_tiles * (uint64_t)bhq, n_two = (uint64_t)((q_tiles + 1) / 2) * (uint64_t)bhq;
+  if (causal) return n_two >= (uint64_t)sms ? 2 : 1;
+  if (n_one <= 2 * (uint64_t)sms) return 2;
+  const double rounds_one = 0.5 * (double)((n_one + sms - 1) / sms);
+  const double rounds_two = 0.92 * (double)((n_two + sms - 1) / sms);
+  return rounds_two <= rounds_one ? 2 : 1;
+}
+
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why) {
   const uint64_t bh = (uint64_t)(p.B * p.H), N_pad = (uint64_t)p.N_pad;
   const uint64_t bhq = (uint64_t)(p.B * p.Hq), Nq = (uint64_t)p.Nq;
@@ -768,13 +786,7 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
   ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;
-  // Which shape.  A two-tile CTA does the work of two one-tile CTAs in about 0.92 of the time the
-  // two take side by side on an SM, but it is handed out in units twice as large.  Non-causal CTAs
-  // all take the same time, so the count of rounds decides: one-tile CTAs go round in half-SM
-  // units (ceil(S / SMs) / 2 rounds for S CTAs), two-tile CTAs in whole ones (ceil(P / SMs) rounds
-  // for P = about S / 2); a call that is resident at once either way is faster with two tiles.
-  // Causal CTAs differ in length and even out by themselves; they take two tiles once there is
-  // such a CTA for every SM.  (The score dump indexes by one-tile CTAs.)
+  // (The score dump indexes by one-tile CTAs, so it keeps that shape.)
   const unsigned q_tiles = (unsigned)((p.Nq + TILE - 1) / TILE);
   static int sm_count[64] = {0};                          // per device, asked once
   int sms = 148, dev = 0;
@@ -784,19 +796,7 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
       sm_count[dev] = 148;
     sms = sm_count[dev];
   }
-  const uint64_t n_one = (uint64_t)q_tiles * bhq, n_two = (uint64_t)((q_tiles + 1) / 2) * bhq;
-  bool two = false;
-  if (q_tiles >= 2 && g_dbg_ptr == nullptr) {
-    if (p.causal) {
-      two = n_two >= (uint64_t)sms;
-    } else if (n_one <= 2 * (uint64_t)sms) {
-      two = true;
-    } else {
-      const double rounds_one = 0.5 * (double)((n_one + sms - 1) / sms);
-      const double rounds_two = 0.92 * (double)((n_two + sms - 1) / sms);
-      two = rounds_two <= rounds_one;
-    }
-  }
+  bool two = g_dbg_ptr == nullptr && choose_tiles_per_cta((int64_t)q_tiles, (int64_t)bhq, p.causal != 0, sms) == 2;
   if (g_force_tiles_per_cta != 0 && g_dbg_ptr == nullptr) two = (g_force_tiles_per_cta == 2);
   dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);

@@ -300,6 +300,11 @@ void sage_debug_score_dump(void* ptr, int key_tile) { sage::set_score_dump(ptr, 
 
 void sage_debug_tiles_per_cta(int n) { sage::set_tiles_per_cta(n); }
 
+int sage_attention_tiles_per_cta(int64_t B, int64_t Hq, int64_t Nq, int causal, int sm_count) {
+  if (B < 1 || Hq < 1 || Nq < 1 || sm_count < 1) return 0;
+  return sage::choose_tiles_per_cta((Nq + sage::TILE - 1) / sage::TILE, B * Hq, causal != 0, sm_count);
+}
+
 size_t sage_workspace_bytes(int64_t B, int64_t H, int64_t N) {
   if (B < 1 || H < 1 || N < 1) return 0;
   const Dims d = {B, H, H, N, N, sage::HD};

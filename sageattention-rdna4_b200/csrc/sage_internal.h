@@ -50,5 +50,6 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
 // Debug aid: subsequent attention launches copy the raw score accumulators of one key tile.
 void set_score_dump(void* ptr, int tile);
 void set_tiles_per_cta(int n);
+int choose_tiles_per_cta(int64_t q_tiles, int64_t bhq, bool causal, int sms);
 
 }  // namespace sage

@@ -51,6 +51,7 @@ SIGNATURES = {
                                          ctypes.c_int, ctypes.c_int, ctypes.c_float, _P]),
     "sage_debug_score_dump": (None, [_P, ctypes.c_int]),
     "sage_debug_tiles_per_cta": (None, [ctypes.c_int]),
+    "sage_attention_tiles_per_cta": (ctypes.c_int, [_I64, _I64, _I64, ctypes.c_int, ctypes.c_int]),
     "sage_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64]),
     "sage_workspace_layout": (ctypes.c_int, [_I64, _I64, _I64, ctypes.POINTER(ctypes.c_size_t)]),
     "sage_attention": (ctypes.c_int, [_P, _P, _P, _P, _P, ctypes.c_size_t, _I64, _I64, _I64,

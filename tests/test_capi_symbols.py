@@ -97,3 +97,23 @@ def test_extended_entry_points_validate_on_the_host():
     assert rc == _native.SAGE_E_ARG and b"null" in lib.sage_last_error()
     rc = lib.sage_prologue_ex(*([p] * 15), 1, 2, 2, 16, 16, 256, 64, s3, s3, s3, 0, 0, 1, None)
     assert rc == _native.SAGE_E_ARG and b"padded key length" in lib.sage_last_error()
+
+
+def test_attention_shape_rule_is_host_arithmetic():
+    """`sage_attention_tiles_per_cta` needs no GPU.  The cases are call sizes on which both shapes
+    were timed on a 148-SM part (one-tile / two-tile ms in the comments)."""
+    lib = _native.load()
+    f = lambda h, n, causal=0, sms=148: lib.sage_attention_tiles_per_cta(1, h, n, causal, sms)
+    assert f(48, 47520) == 2            # the headline shape: 61 rounds either way
+    assert f(48, 1024) == 1             # 0.042 / 0.048: 192 two-tile CTAs are two rounds, the second nearly empty
+    assert f(48, 2048) == 2             # 0.126 / 0.117
+    assert f(12, 6400) == 1             # 0.294 / 0.306
+    assert f(36, 6400) == 2             # 0.727 / 0.712
+    assert f(8, 4096) == 2              # 0.082 / 0.072: resident at once either way
+    assert f(1, 32768) == 2             # 0.568 / 0.475
+    assert f(48, 128) == 1              # a single query tile per head
+    assert f(48, 47520, causal=1) == 2
+    assert f(8, 4096, causal=1) == 1    # fewer two-tile CTAs than SMs
+    assert f(0, 128) == 0 and f(4, 0) == 0 and f(4, 128, sms=0) == 0
+    # more SMs move the thresholds with them
+    assert f(48, 1024, sms=96) == 2 and f(48, 1024, sms=192) == 2
