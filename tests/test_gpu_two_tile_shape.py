@@ -136,3 +136,26 @@ def test_shapes_agree_on_random_calls(force_shape, seed):
     assert torch.isfinite(results[0][0].float()).all()
     assert torch.equal(results[0][0], results[1][0])
     assert torch.equal(results[0][1], results[1][1])
+
+
+@pytest.mark.parametrize("shape", [1, 2])
+def test_a_failure_already_reported_makes_every_cta_return_at_once(force_shape, shape):
+    """The status word is how a CTA whose bounded wait gave up tells the others; CTAs that start
+    with it non-zero must leave without touching the output (and release their TMEM, so that the
+    next launch runs).  Nothing waits here: the word is simply set by the host before the launch."""
+    q, k, v = (t.cuda() for t in _inputs(1, 2, 2, 512, 512, 128, torch.float16, 9))
+    pq = be.quant_qkv(q, k, v)
+    out = torch.full_like(q, 7.0)
+    status = torch.full((1,), 4, dtype=torch.int32, device="cuda")
+    force_shape(shape)
+    be.attn_launch(pq, out, False, 128 ** -0.5, status=status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 4
+    assert bool((out == 7.0).all())
+    status.zero_()
+    be.attn_launch(pq, out, False, 128 ** -0.5, status=status)      # the same SMs serve the next launch
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    force_shape(0)
+    want = be.sage_call(q, k, v, is_causal=False)
+    assert torch.equal(out, want)
