@@ -60,12 +60,16 @@ template <int NQ> struct Shape {
   static constexpr int REGS_SOFTMAX = (NQ == 1) ? 104 : 112;
   static constexpr uint32_t OFF_Q = 0;
   static constexpr uint32_t OFF_K = OFF_Q + NQ * TILE_BYTES;    // 2 stages
-  static constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;     // 2 stages
-  // P tiles per query tile.  With two, the softmax warps write P(j) without waiting for the product
-  // that reads P(j-1), and wait for it only where they need the output accumulator; two one-tile
-  // CTAs would not fit an SM with the second buffer.
-  static constexpr int P_BUFS = (NQ == 2) ? 2 : 1;
-  static constexpr uint32_t OFF_P = OFF_V + 2 * TILE_BYTES;
+  // Two P tiles per query tile: the softmax warps write P(j) without waiting for the product that
+  // reads P(j-1), and wait for it only where they need the output accumulator.  Two one-tile CTAs
+  // share an SM's shared memory, so that shape pays for the second P tile with a single V^T stage:
+  // V^T(j) is fetched once P.V(j-1) has completed, a tile ahead of its use, and the K ring runs
+  // one tile further ahead so that it is not held up behind that wait.
+  static constexpr int V_STAGES = (NQ == 1) ? 1 : 2;
+  static constexpr int K_AHEAD = (NQ == 1) ? 1 : 0;
+  static constexpr int P_BUFS = 2;
+  static constexpr uint32_t OFF_V = OFF_K + 2 * TILE_BYTES;
+  static constexpr uint32_t OFF_P = OFF_V + V_STAGES * TILE_BYTES;
   static constexpr uint32_t OFF_SK = OFF_P + NQ * P_BUFS * TILE_BYTES;   // 4-slot ring of K scales (arrive with the K tile)
   static constexpr uint32_t OFF_SV = OFF_SK + 4 * VEC_BYTES;    // 4-slot ring of staged V factors (same barrier)
   static constexpr uint32_t OFF_BAR = OFF_SV + 4 * VEC_BYTES;
@@ -369,19 +373,27 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_3d(base + OFF_Q + g * TILE_BYTES, &tm_q, bar(BAR_Q), 0, (q_tile0 + g) * TILE, bh);
         const float* sk_row = a.sk + (size_t)bh_kv * a.N_pad;
         const float* sv_row = a.svp + (size_t)bh_kv * a.N_pad;
-        for (int j = 0; j < n_load; ++j) {
+        auto load_k = [&](int j) -> bool {
           const int s = j & 1;
           const uint32_t par = ((uint32_t)(j >> 1) & 1u) ^ 1u;
-          if (!mbar_wait(bar(BAR_KE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
+          if (!mbar_wait(bar(BAR_KE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) return false;
           // The tile's scale rows ride on the K barrier into a 4-slot ring: slot j&3 is rewritten
           // only after QK(j+2) has completed, which needs every softmax warp to be past tile j.
           mbar_expect_tx(bar(BAR_KF + s), TILE_BYTES + 2 * VEC_BYTES);
           tma_load_3d(base + OFF_K + s * TILE_BYTES, &tm_k, bar(BAR_KF + s), 0, j * TILE, bh_kv);
           bulk_load(base + OFF_SK + (j & 3) * VEC_BYTES, sk_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
           bulk_load(base + OFF_SV + (j & 3) * VEC_BYTES, sv_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
-          if (!mbar_wait(bar(BAR_VE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
-          mbar_expect_tx(bar(BAR_VF + s), TILE_BYTES);
-          tma_load_3d(base + OFF_V + s * TILE_BYTES, &tm_v, bar(BAR_VF + s), j * TILE, 0, bh_kv);
+          return true;
+        };
+        bool ok = true;
+        for (int j = 0; ok && j < L::K_AHEAD && j < n_load; ++j) ok = load_k(j);
+        for (int j = 0; ok && j < n_load; ++j) {
+          if (j + L::K_AHEAD < n_load && !load_k(j + L::K_AHEAD)) break;
+          const int sv = j % L::V_STAGES;
+          const uint32_t parv = ((uint32_t)(j / L::V_STAGES) & 1u) ^ 1u;
+          if (!mbar_wait(bar(BAR_VE + sv), parv, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) break;
+          mbar_expect_tx(bar(BAR_VF + sv), TILE_BYTES);
+          tma_load_3d(base + OFF_V + sv * TILE_BYTES, &tm_v, bar(BAR_VF + sv), j * TILE, 0, bh_kv);
         }
       }
     } else if (warp == 1 || (NQ == 2 && warp == 2)) {
@@ -407,8 +419,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             tc_commit(bar(BAR_SF + gb));
           }
           if (j > 0) {
-            const int jj = j - 1, s = jj & 1;
-            ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(jj >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            const int jj = j - 1, s = jj % L::V_STAGES;
+            ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(jj / L::V_STAGES) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
             if (ok) ok = mbar_wait(bar(BAR_PF + gb), (uint32_t)jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
             if (!ok) break;
             tc_fence_after();
@@ -549,16 +561,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float mB_use = (mB_new == -INFINITY) ? 0.f : mB_new;
         const float alphaA = ex2(cqA * (mA - mA_use)), alphaB = ex2(cqB * (mB - mB_use));
 
-        // P.V(j-1) must be complete before the accumulator is rescaled and, with a single P tile,
-        // before P(j) overwrites P(j-1).  With two P tiles the wait moves behind the exponentials,
-        // where it no longer stalls: P(j) goes to the tile P.V(j-2) read, and that product was
-        // waited for in the previous iteration.
-        if (L::P_BUFS == 1 && j > 0) {
-          ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
-          ok = __all_sync(0xffffffffu, ok);
-          if (!ok) break;
-          tc_fence_after();
-        }
         // The accumulator is rescaled after the exponentials, when the score registers are free;
         // PV(j) is not issued before this warp arrives.
         const bool rescale = (j > 0) && __any_sync(0xffffffffu, (mA_new > mA) || (mB_new > mB));
@@ -593,7 +595,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         lA = lA * alphaA + (psA.x + psA.y);                 // this thread's quarter of the row sum
         lB = lB * alphaB + (psB.x + psB.y);
-        if (L::P_BUFS == 2 && j > 0) {
+        // P.V(j-1) must be complete before the accumulator is rescaled.  The wait sits behind the
+        // exponentials, where it does not stall: P(j) went to the tile that P.V(j-2) read, and that
+        // product was waited for in the previous iteration.
+        if (j > 0) {
           ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
