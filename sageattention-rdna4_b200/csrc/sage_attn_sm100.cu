@@ -7,12 +7,13 @@
 //            nearly empty round (see launch_attention).
 //   NQ = 2   two neighbouring query tiles of a head per CTA, 640 threads, one CTA per SM: each K
 //            and V^T tile is loaded once for both, each query tile has its own softmax warps,
-//            TMEM columns, pair of P tiles and MMA-issuing thread.  (Causal: the second tile
+//            TMEM columns, P tiles and MMA-issuing thread.  (Causal: the second tile
 //            visits one key tile more than the first.)
 // Both shapes compute every row with the same instructions in the same order.  Roles inside a CTA:
 //   warp 0     TMA producer: the Q tile(s) once, then a 2-deep ring of K tiles (each carrying that
-//              tile's 128 K scales and 128 staged V factors into a 4-slot ring) and a 2-deep ring
-//              of V^T tiles
+//              tile's 128 K scales and 128 staged V factors into a 4-slot ring) and the V^T tiles
+//              (a 2-deep ring; a single stage for NQ = 1, whose shared memory holds the second P
+//              tile instead)
 //   warp 1     allocates 256 x NQ TMEM columns; one thread issues the tcgen05.mma of query tile 0
 //   warp 2     NQ = 2: one thread issues the tcgen05.mma of query tile 1 (idle for NQ = 1)
 //   warp 3     idle: it completes the first warpgroup, whose registers setmaxnreg hands over
@@ -24,7 +25,8 @@
 //   u  = f32(S) * sk[key]; mask; row max m (in the u domain); s = c_q * u is the log2-domain score
 //   alpha = exp2(c_q*(m_old - m_new)); O *= alpha in TMEM when some row's max moved
 //   p  = exp2(c_q*u - c_q*m); l = l*alpha + sum(p); P8 = e4m3(p * svp[key]) written to shared
-//        memory as unswizzled K-major core matrices, four keys (one 32-bit word) at a time
+//        memory as unswizzled K-major core matrices, four keys (one 32-bit word) at a time; P(j)
+//        and P(j+1) go to different tiles, so P(j+1) is written while P.V(j) still reads P(j)
 // The rows of a K8 tile arrive permuted inside 16-row blocks (the prologue stores them so) to make
 // the four score columns a thread holds of a 16-column block four consecutive keys.
 //   O += P8 . V8            kind::f8f6f4 into 128 more TMEM columns
