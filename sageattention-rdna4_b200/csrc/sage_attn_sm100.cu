@@ -599,7 +599,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         lB = lB * alphaB + (psB.x + psB.y);
         // P.V(j-1) must be complete before the accumulator is rescaled.  The wait sits behind the
         // exponentials, where it does not stall: P(j) went to the tile that P.V(j-2) read, and that
-        // product was waited for in the previous iteration.
+        // product was waited for in the previous iteration.  It is made on every tile, rescaling
+        // or not: it also keeps this warp from arriving at the P barrier of tile j before the MMA
+        // thread has seen the barrier of tile j-1 complete (P.V(j-1) is issued after that), and
+        // the MMA thread's parity wait cannot tell a barrier that is two phases ahead.
         if (j > 0) {
           ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
           ok = __all_sync(0xffffffffu, ok);
