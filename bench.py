@@ -14,8 +14,18 @@ the attention kernel's tensor roofline, the prologue's HBM figure, an end-to-end
 through the public API from pinned host buffers, and a bounded CPU baseline (the oracle, i.e. a
 PyTorch port of the reference's numerics, on the host cores).
 
+Beside the headline line the same JSON object carries: `roofline.peak_8bit_measured` (dense int8
+and e4m3 matrix products of 8192^3 through torch's library calls, burst and sustained, with the SM
+clock each was taken at: the yardstick the attention kernel's fraction is quoted against),
+`config5` (the strong-scaling configuration: B=4, H=48, N=47520, bf16, non-causal, its 192
+(batch, head) units partitioned over the ranks), `other_arms` (the other masking mode, bf16, the
+image-size configurations at N=8771 and the short-call sweep), and with N > 1 `gather_ok` (one
+NCCL all-gather of per-rank outputs outside every timed region).
+
 `--impl reference` times that CPU port alone, with all host threads, on a bounded sample of the
 same workload (the reference's own kernels are AMD gfx1201 binaries and cannot run here).
+`--accuracy` prints the accuracy table instead (CUDA path and oracle against fp32 SDPA, and the
+CUDA path against the oracle, for the five configurations) and exits.
 """
 from __future__ import annotations
 
@@ -37,9 +47,20 @@ import torch  # noqa: E402
 B, H, N, D = 1, 48, 47520, 128
 SEED = 0
 METRIC = "attention TFLOPS (full call incl. quant) at H=48 N=47520 D=128"
-# DRAM bytes of one attention-kernel launch at this workload, from the ncu capture summarised in
-# profiles/attn_fwd_kernel_H16_N16384_fp16_noncausal.md (launch list at the full-size workload: 914 MB read + 554 MB written).
-ATTN_DRAM_TRAFFIC_BYTES = 1.468e9
+# DRAM bytes of one attention-kernel launch, scaled from the ncu capture of the small case
+# (H=16, N=16384: 103.9 MB read + 34.4 MB written against 100.7 + 3 + 67 MB algorithmic, the rest
+# of the output still in L2 when the kernel ends): traffic grows with the operand sizes, so a full
+# launch moves about its algorithmic bytes.  The figure is derived, not measured in this run.
+TRAFFIC_SOURCE = ("derived, not measured in this run: algorithmic bytes x 0.984, the ratio of DRAM bytes to algorithmic "
+                  "bytes in the ncu launch list of profiles/attn_fwd_kernel_H16_N16384_fp16_noncausal.md")
+TRAFFIC_RATIO = 1464.0 / 1488.0
+
+
+def attention_algorithmic_bytes(batch: int = B) -> float:
+    """Compulsory HBM traffic of one attention launch: codes of Q, K, V^T once, the four scale
+    vectors, the output."""
+    bh, n_pad = batch * H, (N + 127) // 128 * 128
+    return bh * N * D + 2 * bh * n_pad * D + 4 * (bh * N + 2 * bh * n_pad) + bh * N * D * 2
 
 
 def flops(causal: bool, batch: int = B) -> float:
@@ -171,6 +192,117 @@ def cpu_baseline(causal: bool, rows: int = 0) -> dict:
                        "%d keys = %.2e of the call's flops, %.1f s" % (H, rows, row0, int(keys), fl / flops(causal), dt))
 
 
+def measure_8bit_peaks(dev, phys_index: int, sustain_s: float = 4.0) -> dict:
+    """Dense 8-bit matrix-product rate of this GPU, the yardstick for the attention kernel: int8
+    (torch._int_mm) and e4m3 (torch._scaled_mm) at 8192^3 through the vendor library, as a burst
+    (best of 10 single launches) and sustained (back to back for about `sustain_s` seconds, where
+    the power cap settles the clock), each with the median SM clock seen while it ran.  Library
+    calls are used here as a measuring stick only; nothing of the product path runs through them."""
+    n = 8192
+    fl = 2.0 * n ** 3
+    res = {"shape": "8192^3", "how": "burst = best of 10 launches (CUDA events); sustained = back to back for ~%.0f s" % sustain_s}
+
+    def rate(name, fn):
+        try:
+            for _ in range(3):
+                fn()
+            torch.cuda.synchronize(dev)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            best = float("inf")
+            with ClockSampler(phys_index) as c0:
+                for _ in range(10):
+                    a.record()
+                    fn()
+                    b.record()
+                    torch.cuda.synchronize(dev)
+                    best = min(best, a.elapsed_time(b))
+            iters = max(10, int(sustain_s * 1e3 / best))
+            with ClockSampler(phys_index) as c1:
+                a.record()
+                for _ in range(iters):
+                    fn()
+                b.record()
+                torch.cuda.synchronize(dev)
+            sus = a.elapsed_time(b) / iters
+            res[name] = dict(burst_tflops=fl / (best * 1e-3) / 1e12, sustained_tflops=fl / (sus * 1e-3) / 1e12,
+                             burst_sm_mhz=c0.summary()["sm_mhz"], sustained_sm_mhz=c1.summary()["sm_mhz"],
+                             sustained_reasons=c1.summary()["reasons"], sustained_iters=iters)
+        except Exception as exc:                       # the library refused the call: say so, measure the rest
+            res[name] = dict(error="%s: %s" % (type(exc).__name__, str(exc)[:200]))
+
+    a8 = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
+    b8 = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev).t()      # column-major operand
+    rate("int8", lambda: torch._int_mm(a8, b8))
+    del a8, b8
+    af = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
+    bf = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
+    one = torch.ones((), dtype=torch.float32, device=dev)
+    rate("e4m3", lambda: torch._scaled_mm(af, bf, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
+    del af, bf
+    return res
+
+
+def mixed_peak(p8: dict, key: str, int8_qk: bool):
+    """Peak of the attention kernel's mix of products: Q.K^T in int8 (fp16 inputs) or e4m3 (bf16
+    inputs) and P.V in e4m3, half of the flops each, so the harmonic mean of the two rates."""
+    try:
+        qk = p8["int8" if int8_qk else "e4m3"][key]
+        pv = p8["e4m3"][key]
+        return 2.0 / (1.0 / qk + 1.0 / pv)
+    except (KeyError, TypeError, ZeroDivisionError):
+        return None
+
+
+def config5_block(dev, world: int, rank: int, steps: int, sync_all, max_over_ranks) -> dict:
+    """The scaling configuration as written: B=4, H=48, N=47520, D=128, bf16, non-causal,
+    smooth_k on, Q, K, V ~ N(0,1).  Its 192 (batch, head) units are partitioned over the ranks
+    (192 / 96 / 48 / 24 units per GPU at 1 / 2 / 4 / 8 GPUs: total work fixed, strong scaling); no
+    collective on the data path.  Timed with CUDA events between barriers, max over ranks."""
+    import sageattention
+    from sageattention.sharding import partition_units, sageattn_sharded
+    units_total = 4 * H
+    lo, hi = partition_units(units_total, world, rank)
+    u = hi - lo
+    g = torch.Generator(device=dev).manual_seed(5000 + lo)
+    q, k, v = (torch.randn(1, u, N, D, generator=g, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    for _ in range(2):
+        out = sageattn_sharded(q, k, v, is_causal=False)
+    sync_all()
+    n_steps = max(3, min(steps, 5))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(n_steps):
+        out = sageattn_sharded(q, k, v, is_causal=False)
+    e1.record()
+    sync_all()
+    ms = max_over_ranks(e0.elapsed_time(e1)) / n_steps
+    finite = bool(torch.isfinite(out[0, 0].float()).all().item())
+    del q, k, v, out
+    total = 4.0 * units_total * N * N * D / (ms * 1e-3) / 1e12
+    return dict(workload="B=4 H=%d N=%d D=%d bf16 non-causal smooth_k: %d (batch, head) units, %d on this rank"
+                         % (H, N, D, units_total, u),
+                scaling="strong", units_total=units_total, units_rank0=u, steps=n_steps, ms_per_step=ms,
+                tflops_total=total, tflops_per_gpu=total / world, output_finite=finite)
+
+
+def gather_check(dev, world: int, rank: int) -> bool:
+    """One all-gather of per-rank outputs over NCCL, outside every timed region: every rank
+    computes its partition of a small replicated call, the outputs are gathered, and the result
+    must equal the same call computed whole on this rank, bit for bit (units are independent)."""
+    import torch.distributed as dist
+    import sageattention
+    from sageattention.sharding import partition_units, sageattn_sharded
+    units = 2 * world + 1                                # ragged: the first rank takes one more
+    g = torch.Generator().manual_seed(77)
+    q, k, v = (torch.randn(1, units, 300, D, generator=g).half().to(dev) for _ in range(3))
+    lo, hi = partition_units(units, world, rank)
+    got = sageattn_sharded(q[:, lo:hi], k[:, lo:hi], v[:, lo:hi], is_causal=True, gather=True)
+    whole = sageattention.sageattn(q, k, v, is_causal=True)
+    ok = torch.tensor([1 if (got.shape == whole.shape and torch.equal(got, whole)) else 0], device=dev)
+    dist.all_reduce(ok, op=dist.ReduceOp.MIN)
+    return bool(ok.item())
+
+
 def other_arms(q, k, v, dev, causal_main: bool) -> dict:
     """Full-call numbers for the arms the headline does not cover: the other masking mode, bf16
     inputs (e4m3 Q.K), and the short-call sweep of the configurations (fp16, H=48, non-causal,
@@ -197,6 +329,18 @@ def other_arms(q, k, v, dev, causal_main: bool) -> dict:
         ms = timed(lambda: sageattention.sageattn(qb, kb, vb, is_causal=c), 3)
         out["bf16_%s" % ("causal" if c else "non_causal")] = dict(ms=ms, tflops=flops(c) / (ms * 1e-3) / 1e12)
     del qb, kb, vb
+    # the image-size configurations (N = 8771): fp16 non-causal with a per-channel K bias and
+    # per-head Q/K multipliers; bf16 causal with the K bias.  20 calls back to back.
+    from oracle import ref_numerics as R               # input generator only
+    n_img = 8771
+    fl_img = 4.0 * H * n_img * n_img * D
+    q2, k2, v2 = (t.to(dev) for t in R.make_inputs(1, H, n_img, D, torch.float16, seed=SEED, k_bias_std=1.0, head_scale=True))
+    ms = timed(lambda: sageattention.sageattn(q2, k2, v2, is_causal=False), 20)
+    out["config2_image_size_fp16_non_causal_n8771"] = dict(ms=ms, tflops=fl_img / (ms * 1e-3) / 1e12)
+    q3, k3, v3 = (t.to(dev) for t in R.make_inputs(1, H, n_img, D, torch.bfloat16, seed=SEED, k_bias_std=1.0))
+    ms = timed(lambda: sageattention.sageattn(q3, k3, v3, is_causal=True), 20)
+    out["config3_image_size_bf16_causal_n8771"] = dict(ms=ms, tflops=0.5 * fl_img / (ms * 1e-3) / 1e12)
+    del q2, k2, v2, q3, k3, v3
     short = {}
     for n in (288, 512, 1024, 4096):
         qs, ks, vs = (t[:, :, :n].contiguous() for t in (q, k, v))
@@ -234,6 +378,62 @@ def other_arms(q, k, v, dev, causal_main: bool) -> dict:
                                   / (ms * 1e-3) / 1e12)
     out["wider_call_shapes"] = wide
     return out
+
+
+def run_accuracy() -> int:
+    """Accuracy table of the CUDA path on the benchmark configurations: cosine / relative L1 /
+    relative RMS against fp32 SDPA, the oracle's own error against SDPA beside it, and the CUDA
+    path against the oracle evaluated with the kernel's 128-key tile and with the reference's
+    64-key tile.  The oracle and SDPA are evaluated by torch on the device; for the large
+    configurations on a subset of heads (the call itself runs with all heads).  One JSON line."""
+    import sageattention
+    from oracle import ref_numerics as R
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    rows = []
+
+    def add(name, q, k, v, causal, heads):
+        out = sageattention.sageattn(q, k, v, is_causal=causal)
+        torch.cuda.synchronize(dev)
+        sl = torch.tensor(heads, device=dev)
+        qs, ks, vs, os_ = q[:, sl], k[:, sl], v[:, sl], out[:, sl]
+        ref = R.sdpa_fp32(qs, ks, vs, is_causal=causal)
+        o128 = R.sageattn_oracle(qs, ks, vs, is_causal=causal, tile=128)
+        o64 = R.sageattn_oracle(qs, ks, vs, is_causal=causal, tile=64)
+        m = lambda a, b: dict(cos=R.cosine(a, b), rel_l1=R.rel_l1(a, b), rel_rms=R.rel_rms(a, b))
+        rows.append(dict(config=name, heads_compared=len(heads), cuda_vs_sdpa=m(os_, ref), oracle64_vs_sdpa=m(o64, ref),
+                         cuda_vs_oracle128=m(os_, o128), cuda_vs_oracle64=m(os_, o64)))
+
+    to = lambda ts: tuple(t.to(dev) for t in ts)
+    add("1: B=1 H=4 N=512 fp16 non-causal, K bias 0.5", *to(R.make_inputs(1, 4, 512, D, torch.float16, seed=0, k_bias_std=0.5)),
+        False, [0, 1, 2, 3])
+    add("2: B=1 H=48 N=8771 fp16 non-causal, K bias 1, head multipliers",
+        *to(R.make_inputs(1, 48, 8771, D, torch.float16, seed=0, k_bias_std=1.0, head_scale=True)), False, [0, 15, 31, 47])
+    add("3: B=1 H=48 N=8771 bf16 causal, K bias 1",
+        *to(R.make_inputs(1, 48, 8771, D, torch.bfloat16, seed=0, k_bias_std=1.0)), True, [0, 15, 31, 47])
+    q, k, v = to(R.make_inputs(1, 48, 47520, D, torch.float16, seed=0, outlier_frac=0.001))
+    for dt in (torch.float16, torch.bfloat16):
+        for causal in (False, True):
+            add("4: B=1 H=48 N=47520 %s %s, 0.1%% K tokens x50" % ("fp16" if dt == torch.float16 else "bf16",
+                                                                    "causal" if causal else "non-causal"),
+                q.to(dt), k.to(dt), v.to(dt), causal, [0, 47])
+    del q, k, v
+    g = torch.Generator(device=dev).manual_seed(5)
+    q, k, v = (torch.randn(4, 48, 47520, D, generator=g, device=dev, dtype=torch.bfloat16) for _ in range(3))
+    out = sageattention.sageattn(q, k, v)
+    torch.cuda.synchronize(dev)
+    qs, ks, vs, os_ = q[3:4, 46:48], k[3:4, 46:48], v[3:4, 46:48], out[3:4, 46:48]
+    ref = R.sdpa_fp32(qs, ks, vs)
+    o128 = R.sageattn_oracle(qs, ks, vs, tile=128)
+    o64 = R.sageattn_oracle(qs, ks, vs, tile=64)
+    m = lambda a, b: dict(cos=R.cosine(a, b), rel_l1=R.rel_l1(a, b), rel_rms=R.rel_rms(a, b))
+    rows.append(dict(config="5: B=4 H=48 N=47520 bf16 non-causal (units 190, 191 of 192)", heads_compared=2,
+                     cuda_vs_sdpa=m(os_, ref), oracle64_vs_sdpa=m(o64, ref), cuda_vs_oracle128=m(os_, o128),
+                     cuda_vs_oracle64=m(os_, o64)))
+    print(json.dumps(dict(accuracy=rows, note="oracle = PyTorch restatement of the reference numerics; "
+                                              "tolerance bars: vs oracle128 cos>=0.9999 rel_l1<=5e-3, vs oracle64 "
+                                              "cos>=0.9995 rel_l1<=2e-2, vs SDPA rel_rms<0.08")))
+    return 0
 
 
 def run_reference(args) -> int:
@@ -274,6 +474,9 @@ def main() -> int:
     ap.add_argument("--causal", action="store_true")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extras", action="store_true", help="skip the causal / bf16 / short-call arms")
+    ap.add_argument("--no-peak", action="store_true", help="skip the dense 8-bit peak measurement")
+    ap.add_argument("--no-config5", action="store_true", help="skip the strong-scaling configuration")
+    ap.add_argument("--accuracy", action="store_true", help="print the accuracy table and exit")
     ap.add_argument("--e2e-groups", type=int, default=0,
                     help="head groups a step of the end-to-end pipeline is issued as (0: the default)")
     ap.add_argument("--shape", default=None, metavar="H,N",
@@ -285,6 +488,8 @@ def main() -> int:
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
+    if args.accuracy:
+        return run_accuracy()
 
     import torch.distributed as dist
     import sageattention
@@ -367,13 +572,30 @@ def main() -> int:
     torch.cuda.synchronize(dev)
     pro = ev[0].elapsed_time(ev[1]) / args.steps
     pk = peaks()
-    peak8 = 2.0 * pk["bf16_tflops_sustained"]
     achieved = flops(causal) / (att * 1e-3) / 1e12
+    # The yardstick: this GPU's own dense 8-bit rate, measured in this run on rank 0 (the other
+    # ranks wait).  The kernel's products are half int8 (Q.K^T) and half e4m3 (P.V).
+    p8 = measure_8bit_peaks(dev, physical_gpu_index(local)) if (rank == 0 and not args.no_peak) else None
+    if world > 1:
+        dist.barrier()
+    burst = mixed_peak(p8, "burst_tflops", True) if p8 else None
+    sustained = mixed_peak(p8, "sustained_tflops", True) if p8 else None
+    if burst:
+        peak8, basis = burst, ("measured in this run: harmonic mean of the int8 and e4m3 8192^3 burst rates "
+                               "(torch._int_mm / torch._scaled_mm); a launch is timed alone, so the burst figure")
+    else:
+        peak8, basis = 2.0 * pk["bf16_tflops"], "2 x bf16_tflops burst (%s) of MEASURED_PEAKS.json: no 8-bit figure measured in this run" % pk["source"]
     roofline = dict(bound="tensor", kernel="attn_fwd_kernel", achieved=achieved, peak=peak8, unit="TFLOP/s",
-                    frac=achieved / peak8, traffic=(ATTN_DRAM_TRAFFIC_BYTES if (not causal and not args.shape) else None), ms_per_launch=att,
-                    peak_basis="2 x bf16_tflops_sustained (%s) of MEASURED_PEAKS.json: dense 8-bit rate is twice bf16; "
-                               "vs 2 x burst %.0f: %.3f; vs nominal 4500: %.3f"
-                               % (pk["source"], 2 * pk["bf16_tflops"], achieved / (2 * pk["bf16_tflops"]), achieved / 4500.0))
+                    frac=achieved / peak8, ms_per_launch=att, peak_basis=basis,
+                    peak_8bit_measured=p8,
+                    frac_vs_measured_sustained=(achieved / sustained) if sustained else None,
+                    frac_vs_2x_bf16_burst=achieved / (2 * pk["bf16_tflops"]),
+                    frac_vs_2x_bf16_sustained=achieved / (2 * pk["bf16_tflops_sustained"]),
+                    frac_vs_nominal_4500=achieved / 4500.0,
+                    bf16_peaks_file=dict(source=pk["source"], burst=pk["bf16_tflops"], sustained=pk["bf16_tflops_sustained"]),
+                    traffic=(attention_algorithmic_bytes() * TRAFFIC_RATIO) if not causal else None,
+                    traffic_source=TRAFFIC_SOURCE,
+                    algorithmic_bytes=attention_algorithmic_bytes())
     pro_gbs = prologue_bytes() / (pro * 1e-3) / 1e9
     prologue = dict(bound="hbm", kernel="kmean_kernel + quant_qkv_kernel (+ memset)", achieved=pro_gbs, peak=pk["hbm_gbs"],
                     unit="GB/s", frac=pro_gbs / pk["hbm_gbs"], ms=pro, algorithmic_bytes=prologue_bytes())
@@ -456,8 +678,14 @@ def main() -> int:
                h2d_bytes_per_step=3 * nbytes, d2h_bytes_per_step=nbytes,
                how="copy-in, copy-out and two compute streams, two sets of device buffers; a step is issued as %d "
                    "head groups through the public API so that copies of one group overlap the calls of the others" % GROUPS,
+               host_copy_gbs_per_rank=4 * nbytes / (e2e_ms * 1e-3) / 1e9,
+               host_copy_gbs_aggregate=world * 4 * nbytes / (e2e_ms * 1e-3) / 1e9,
                host_affinity=affinity, serial_ms_per_step=e2e_serial_ms,
                serial_value=flops(causal, B * world) / (e2e_serial_ms * 1e-3) / 1e12)
+
+    # ---- the scaling configuration (strong scaling over the 192 units) and the NCCL gather ----
+    c5 = None if (args.shape or args.no_config5) else config5_block(dev, world, rank, args.steps, sync_all, max_over_ranks)
+    gather_ok = gather_check(dev, world, rank) if world > 1 else None
 
     # ---- the other arms of the configurations (informative; N = 1 only) ----
     others = None
@@ -472,6 +700,10 @@ def main() -> int:
                     dtype="int8+fp8", data="synthetic", config=workload_config(causal, world),
                     roofline=roofline, prologue=prologue, e2e=e2e, gpu_launches=3 * args.steps,
                     clocks=clk.summary(), kernel_status=status)
+        if c5 is not None:
+            line["config5"] = c5
+        if gather_ok is not None:
+            line["gather_ok"] = gather_ok
         if others is not None:
             line["other_arms"] = others
         if not args.no_cpu_baseline and world == 1:

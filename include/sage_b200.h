@@ -75,6 +75,9 @@ size_t sage_prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
  *             ran out (the outputs are then undefined); sage_attention reports the same event as
  *             bit 8 of its status word
  *   N_pad     must equal sage_pad_len(N)
+ * Alignment: q, k, v, q8, k8, v8t, sk, sv, svp and ctrl (and vmean of sage_prologue_ex) are read or
+ * written with 16-byte vector accesses and must be 16-byte aligned; a misaligned one is refused
+ * with SAGE_E_ARG before anything is launched.  sq, s_fold, mean and qm need 4-byte alignment.
  * Two kernel launches (mean, quantise) and one small memset. */
 int sage_prologue(const void* q, const void* k, const void* v,
                   void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
@@ -100,7 +103,12 @@ int sage_prologue(const void* q, const void* k, const void* v,
  *   - All calls on a device share the one array, and it keeps the previous call's contents; the
  *     words that must start at zero are cleared on the stream at the start of each call.  Two
  *     calls whose GPU work overlaps (different streams, no ordering between them) race on it:
- *     order them, or give one of them its own scratch through sage_prologue. */
+ *     order them, or give one of them its own scratch through sage_prologue.
+ *   - `status` (optional, may be NULL): one int32 in the caller's device memory.  The quantiser's
+ *     own failure flag lives inside the built-in array, which the caller cannot read, so a
+ *     bounded wait that ran out is reported here instead: bit 8 (0x100) is ORed into the word and
+ *     the outputs of that call are undefined.  The call never clears the word; zero it once and
+ *     read it whenever the stream is known to have passed the call. */
 size_t sage_prologue_static_ctrl_capacity(void);
 int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
                               void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv,
@@ -108,7 +116,7 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
                               int64_t B, int64_t H, int64_t N, int64_t N_pad,
                               const int64_t q_strides[3], const int64_t k_strides[3],
                               const int64_t v_strides[3],
-                              int dtype, int qk_mode, int smooth_k, void* stream);
+                              int dtype, int qk_mode, int smooth_k, int32_t* status, void* stream);
 
 /* The attention kernel on quantised operands.
  *
@@ -120,22 +128,30 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
  *              o_strides, last axis contiguous, strides multiples of 8, 16-byte aligned base.
  *   status     one int32 in device memory, zero before the call; the kernel ORs in a non-zero
  *              code if one of its bounded waits gave up (the output is then undefined).
- * The operands are the prologue's outputs for the same B, H, N, N_pad, qk_mode. */
+ *   sm_scale   finite and > 0 (anything else is refused with SAGE_E_ARG: the kernel takes the row
+ *              maximum before it applies the scale).
+ * The operands are the prologue's outputs for the same B, H, N, N_pad, qk_mode; q8, k8, v8t, sk,
+ * svp, out (and vmean of sage_attn_fwd_ex) must be 16-byte aligned. */
 int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* sk,
                   const void* v8t, const float* svp, const float* s_fold, void* out,
                   int64_t B, int64_t H, int64_t N, int64_t N_pad, const int64_t o_strides[3],
                   int causal, float sm_scale, int out_dtype, int qk_mode,
                   int32_t* status, void* stream);
 
-/* Debugging aid (process-global, not thread-safe): while `ptr` is non-null every later attention
- * launch copies the raw Q.K^T accumulators (int32, or fp32 bits for e4m3 codes) of key tile
- * `key_tile` to ptr[((bh * q_tiles + q_tile) * 128 + row) * 128 + key].  Pass NULL to stop. */
-void sage_debug_score_dump(void* ptr, int key_tile);
+/* Enqueue, on `stream`, a copy of one status word (device memory: the `status` of sage_attn_fwd,
+ * or the word at offset 10 of sage_workspace_layout) into `status_host`, which should be pinned
+ * host memory so that the copy does not block.  Nothing synchronises: once the stream has passed
+ * this point the host word holds the call's status, non-zero after a bounded wait ran out.  This
+ * is how a host learns of a device-side failure without waiting for every call; the reference
+ * raises for such failures only in strict mode and otherwise falls back
+ * (sageattention/sk1_backend/__init__.py:1022-1027,1114-1123).  Status bits: 1 TMA producer,
+ * 2 MMA issuer, 4 softmax warp of the attention kernel; 0x100 tile load of the prologue. */
+int sage_status_mirror(const int32_t* status_dev, int32_t* status_host, void* stream);
 
-/* Debugging aid (process-global, not thread-safe): the attention kernel has two shapes, one or two
+/* Test hook (one process-wide atomic word): the attention kernel has two shapes, one or two
  * 128-query tiles per CTA, and picks the one it expects to finish sooner for the call's size.
- * n = 1 or 2 forces that shape for later launches, anything else restores the automatic
- * choice.  Both shapes give bit-identical results. */
+ * n = 1 or 2 forces that shape for later launches from any thread, anything else restores the
+ * automatic choice.  Both shapes give bit-identical results. */
 void sage_debug_tiles_per_cta(int n);
 
 /* The shape the attention kernel takes, left to itself, for B x Hq heads of Nq queries on a device

@@ -43,8 +43,41 @@
 // TMEM, and CTAs that start later return at once.
 #include <cuda.h>
 
+#include <atomic>
+
 #include "sage_common.cuh"
 #include "sage_internal.h"
+
+// experiment knobs (defaults = shipped behaviour)
+#ifndef SAGE_SMEM_PLAIN
+#define SAGE_SMEM_PLAIN 0
+#endif
+#ifndef SAGE_LEAN_MMA
+#define SAGE_LEAN_MMA 0
+#endif
+#ifndef SAGE_POLY
+#define SAGE_POLY 0
+#endif
+#ifndef SAGE_PREFETCH
+#define SAGE_PREFETCH 0
+#endif
+// start the four softmax warps of a scheduler a quarter period apart (cycles per step; 0 = off)
+#ifndef SAGE_STAGGER
+#define SAGE_STAGGER 0
+#endif
+// timing-only ablations (wrong results): 1 no P stores, 2 no scale loads, 4 no P.V products, 8 no ex2
+#ifndef SAGE_ABL
+#define SAGE_ABL 0
+#endif
+
+#ifndef SAGE_SCALAR
+#define SAGE_SCALAR 0
+#endif
+#if SAGE_SCALAR
+#define __fmul2_rn(a, b) make_float2(__fmul_rn((a).x, (b).x), __fmul_rn((a).y, (b).y))
+#define __fadd2_rn(a, b) make_float2(__fadd_rn((a).x, (b).x), __fadd_rn((a).y, (b).y))
+#define __ffma2_rn(a, b, c) make_float2(__fmaf_rn((a).x, (b).x, (c).x), __fmaf_rn((a).y, (b).y, (c).y))
+#endif
 
 namespace sage {
 
@@ -203,6 +236,30 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
   }
 }
 
+// The same with the two 64-bit descriptors handed over as 32-bit halves (the upper halves are
+// compile-time constants, the lower ones differ by small constants between the k-steps).
+template <bool INT8>
+__device__ __forceinline__ void mma_ss_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
+                                              uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
+  if (INT8) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+  } else {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
+  }
+}
+constexpr uint32_t DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
+constexpr uint32_t DESC_HI_NOSW = (1024u >> 4) | (1u << 14);
+__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
+__device__ __forceinline__ uint32_t desc_lo_nosw(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | ((128u >> 4) << 16); }
+
 // 16 lanes x 256 bits per repetition: thread t holds lanes t/4 (registers 4i, 4i+1) and t/4 + 8
 // (registers 4i+2, 4i+3), columns 8i + 2(t%4) and the next one; x8 = 64 columns, 32 registers.
 __device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t* r) {
@@ -247,6 +304,22 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return y;
 }
 
+// 2^t for two arguments t <= 0 on the FMA pipe: split t = n + f with n integral and |f| <= 1/2
+// (adding 1.5 * 2^23 leaves n in the low mantissa bits), a cubic for 2^f (relative error 7.5e-5)
+// and n added to the exponent field.  Arguments below -126 (masked scores are -inf) give 2^-126.
+__device__ __forceinline__ float2 ex2_poly2(float2 t) {
+  const float MAGIC = 12582912.f;
+  const float2 tc = make_float2(fmaxf(t.x, -126.f), fmaxf(t.y, -126.f));
+  const float2 r = __fadd2_rn(tc, make_float2(MAGIC, MAGIC));
+  const float2 nf = __fadd2_rn(r, make_float2(-MAGIC, -MAGIC));
+  const float2 f = __fadd2_rn(tc, make_float2(-nf.x, -nf.y));
+  float2 q = __ffma2_rn(f, make_float2(0.055171460f, 0.055171460f), make_float2(0.24261086f, 0.24261086f));
+  q = __ffma2_rn(q, f, make_float2(0.69326097f, 0.69326097f));
+  q = __ffma2_rn(q, f, make_float2(0.99992812f, 0.99992812f));
+  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(r.x) << 23)),
+                     __int_as_float(__float_as_int(q.y) + (__float_as_int(r.y) << 23)));
+}
+
 // Shared-memory matrix descriptor of a K-major tile of 128-byte rows written with the 128-byte
 // swizzle (what TMA SWIZZLE_128B produces): 8-row groups 1024 bytes apart, descriptor version 1.
 __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t saddr) {
@@ -275,8 +348,6 @@ struct AttnKArgs {
   long long o_sb, o_sh, o_sr;
   float sm_scale;
   int32_t* status;
-  uint32_t* dbg;      // when non-null: raw score accumulators of key tile `dbg_tile` are copied here
-  int dbg_tile;
 };
 
 template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -397,6 +468,54 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int g = warp - 1;
       const int gb = BAR_PER_TILE * g;
       const int n_tiles = tiles_of(g);
+#if SAGE_LEAN_MMA
+      if (lane == 0) {
+        constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
+        // Lower halves of the operand descriptors: a tile (stage, P buffer) further is +1024 in
+        // the address field, a k-step +2 (32 bytes of a swizzled row) or +16 (256 bytes: two
+        // 16-byte columns of the unswizzled P tile).
+        const uint32_t q_lo = desc_lo_sw128(base + OFF_Q + g * TILE_BYTES);
+        const uint32_t k_lo = desc_lo_sw128(base + OFF_K);
+        const uint32_t v_lo = desc_lo_sw128(base + OFF_V);
+        const uint32_t p_lo = desc_lo_nosw(base + OFF_P + g * L::P_BUFS * TILE_BYTES);
+        const uint32_t d_s = tmem + L::tmem_s(g), d_o = tmem + L::tmem_o(g);
+        const uint32_t b_kf = bar(BAR_KF), b_ke = bar(BAR_KE), b_vf = bar(BAR_VF), b_ve = bar(BAR_VE);
+        const uint32_t b_sf = bar(BAR_SF + gb), b_sfree = bar(BAR_SFREE + gb), b_pf = bar(BAR_PF + gb), b_pv = bar(BAR_PV + gb);
+        bool ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
+        for (int j = 0; ok && j <= n_tiles; ++j) {
+          if (j < n_tiles) {
+            const uint32_t s = (uint32_t)j & 1u;
+            ok = mbar_wait(b_kf + 8u * s, ((uint32_t)j >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok && j > 0) ok = mbar_wait(b_sfree, (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t kl = k_lo + 1024u * s;
+            mma_ss_halves<INT8>(d_s, q_lo + 0, DESC_HI_SW128, kl + 0, DESC_HI_SW128, IDESC_QK, 0u);
+            mma_ss_halves<INT8>(d_s, q_lo + 2, DESC_HI_SW128, kl + 2, DESC_HI_SW128, IDESC_QK, 1u);
+            mma_ss_halves<INT8>(d_s, q_lo + 4, DESC_HI_SW128, kl + 4, DESC_HI_SW128, IDESC_QK, 1u);
+            mma_ss_halves<INT8>(d_s, q_lo + 6, DESC_HI_SW128, kl + 6, DESC_HI_SW128, IDESC_QK, 1u);
+            tc_commit(b_ke + 8u * s);
+            tc_commit(b_sf);
+          }
+          if (j > 0) {
+            const uint32_t jj = (uint32_t)(j - 1);
+            const uint32_t s = (L::V_STAGES == 2) ? (jj & 1u) : 0u;
+            const uint32_t parv = (L::V_STAGES == 2) ? ((jj >> 1) & 1u) : (jj & 1u);
+            ok = mbar_wait(b_vf + 8u * s, parv, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok) ok = mbar_wait(b_pf, jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+            const uint32_t pl = p_lo + 1024u * (jj & 1u), vl = v_lo + 1024u * s;
+            mma_ss_halves<false>(d_o, pl + 0, DESC_HI_NOSW, vl + 0, DESC_HI_SW128, IDESC_F8, jj > 0 ? 1u : 0u);
+            mma_ss_halves<false>(d_o, pl + 16, DESC_HI_NOSW, vl + 2, DESC_HI_SW128, IDESC_F8, 1u);
+            mma_ss_halves<false>(d_o, pl + 32, DESC_HI_NOSW, vl + 4, DESC_HI_SW128, IDESC_F8, 1u);
+            mma_ss_halves<false>(d_o, pl + 48, DESC_HI_NOSW, vl + 6, DESC_HI_SW128, IDESC_F8, 1u);
+            tc_commit(b_ve + 8u * s);
+            tc_commit(b_pv);
+          }
+        }
+      }
+#else
       if (lane == 0) {
         constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
         bool ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
@@ -421,7 +540,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < 4; ++k)
+            for (int k = 0; k < ((SAGE_ABL & 4) ? 0 : 4); ++k)
               mma_ss<false>(tmem + L::tmem_o(g),
                             kmajor_nosw_desc(base + OFF_P + (g * L::P_BUFS + (jj & (L::P_BUFS - 1))) * TILE_BYTES + 256 * k),
                             kmajor_sw128_desc(base + OFF_V + s * TILE_BYTES + 32 * k), IDESC_F8,
@@ -431,6 +550,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
+#endif
     } else if (warp >= 4) {
       // ------------------------------- softmax warps ------------------------------
       // A warp owns 16 TMEM lanes (query rows) and all 128 key columns, read with the 16x256b
@@ -470,33 +590,65 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         ok = mbar_wait(bar(BAR_SF + gb), (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
+#if SAGE_STAGGER
+        if (j == 0) {
+          const long long hold = (long long)SAGE_STAGGER * (long long)(2 * g + sub);
+          const long long t0 = clock64();
+          while (clock64() - t0 < hold) { }
+        }
+#endif
         tc_fence_after();
         uint32_t acc[64];                                   // acc[8m + {0,1,4,5}]: row A keys +0..3; {2,3,6,7}: row B
+#if SAGE_ABL & 256
+#pragma unroll
+        for (int i = 0; i < 64; ++i) acc[i] = (uint32_t)(j + i);
+#else
         tmem_ld_16x256b_x16(t_s, acc);
         tmem_ld_wait();
+#endif
         tc_fence_before();
         __syncwarp();
         mbar_arrive_lane0(bar(BAR_SFREE + gb), lane);
-        if (a.dbg != nullptr && j == a.dbg_tile) {
-          uint32_t* dA = a.dbg + (((size_t)bh * gridDim.x + q_tile) * TILE + rowA) * TILE + 4 * c;
-          uint32_t* dB = dA + 8 * TILE;
+#if SAGE_ABL & 128
+        {
+          uint32_t x = 0;
 #pragma unroll
-          for (int m = 0; m < 8; ++m) {
-            dA[16 * m + 0] = acc[8 * m + 0]; dA[16 * m + 1] = acc[8 * m + 1];
-            dA[16 * m + 2] = acc[8 * m + 4]; dA[16 * m + 3] = acc[8 * m + 5];
-            dB[16 * m + 0] = acc[8 * m + 2]; dB[16 * m + 1] = acc[8 * m + 3];
-            dB[16 * m + 2] = acc[8 * m + 6]; dB[16 * m + 3] = acc[8 * m + 7];
+          for (int i = 0; i < 64; ++i) x ^= acc[i];
+          if (x == 0x12345678u) lA += 1.f;                  // keeps the loads alive
+          if (j > 0) {
+            ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            tc_fence_after();
           }
+          fence_async_smem();
+          tc_fence_before();
+          __syncwarp();
+          mbar_arrive_lane0(bar(BAR_PF + gb), lane);
+          continue;
         }
+#endif
 
         const uint32_t skv = sk_c + (uint32_t)(j & 3) * VEC_BYTES;        // this tile's K scales
         const uint32_t svv = skv + (OFF_SV - OFF_SK);                      // and its staged V factors
+#if SAGE_SMEM_PLAIN
+        const uint8_t* sk_ptr = gbase + OFF_SK + 16 * c + (j & 3) * VEC_BYTES;
+        const uint8_t* sv_ptr = sk_ptr + (OFF_SV - OFF_SK);
+        uint8_t* pA_ptr = gbase + OFF_P + (g * L::P_BUFS + (j & (L::P_BUFS - 1))) * TILE_BYTES + lane_base * 128 + 16 * r0 + 4 * c;
+        uint8_t* pB_ptr = pA_ptr + 8 * 128;
+#endif
         float2 uA[16], uB[16];                              // u[2m], u[2m+1]: keys 16m+4c+{0,1}, +{2,3} (times sk)
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
+#if SAGE_ABL & 2
+          const float4 kk = make_float4(cqA, cqB, cqA, cqB);
+#elif SAGE_SMEM_PLAIN
+          const float4 kk = *reinterpret_cast<const float4*>(sk_ptr + 64 * m);
+#else
           const float4 kk = lds128(skv + 64 * m);
+#endif
           float a0, a1, a2, a3, b0, b1, b2, b3;
-          if (INT8) {
+          if (INT8 && !(SAGE_ABL & 16)) {
             a0 = (float)(int)acc[8 * m + 0]; a1 = (float)(int)acc[8 * m + 1];
             b0 = (float)(int)acc[8 * m + 2]; b1 = (float)(int)acc[8 * m + 3];
             a2 = (float)(int)acc[8 * m + 4]; a3 = (float)(int)acc[8 * m + 5];
@@ -538,7 +690,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         float xa0 = uA[0].x, xa1 = uA[0].y, xb0 = uB[0].x, xb1 = uB[0].y;
 #pragma unroll
-        for (int i = 1; i < 16; i += 2) {
+        for (int i = 1; i < ((SAGE_ABL & 32) ? 0 : 16); i += 2) {
           xa0 = max3(xa0, uA[i].x, uA[i].y);
           xb0 = max3(xb0, uB[i].x, uB[i].y);
           if (i + 1 < 16) {
@@ -566,28 +718,71 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float nmA = -(cqA * mA_use), nmB = -(cqB * mB_use);
         const float2 nmA2 = make_float2(nmA, nmA), nmB2 = make_float2(nmB, nmB);
         float2 psA = make_float2(0.f, 0.f), psB = make_float2(0.f, 0.f);
+        auto load_sv = [&](int m) -> float4 {
+#if SAGE_ABL & 2
+          return make_float4(cqB, cqA, cqB, cqA);
+#elif SAGE_SMEM_PLAIN
+          return *reinterpret_cast<const float4*>(sv_ptr + 64 * m);
+#else
+          return lds128(svv + 64 * m);
+#endif
+        };
+        // exponentials of a pair of scores; some pairs are evaluated on the FMA pipe
+        auto exp_pair = [&](float2 t, bool poly) -> float2 {
+#if SAGE_ABL & 8
+          return make_float2(t.x * t.x + 1.f, t.y * t.y + 1.f);
+#endif
+          if (!poly) return make_float2(ex2(t.x), ex2(t.y));
+          return ex2_poly2(t);
+        };
+#if SAGE_PREFETCH
+        float4 vv_next = load_sv(0);
+#endif
 #pragma unroll
         for (int m = 0; m < 8; ++m) {                       // 16 keys = one 16-byte chunk of a P row; 4 of them here
-          const float4 vv = lds128(svv + 64 * m);
+#if SAGE_PREFETCH
+          const float4 vv = vv_next;
+          if (m + 1 < 8) vv_next = load_sv(m + 1);
+#else
+          const float4 vv = load_sv(m);
+#endif
           const float2 v01 = make_float2(vv.x, vv.y), v23 = make_float2(vv.z, vv.w);
+          uint32_t wA, wB;
           {
             const float2 t0 = __ffma2_rn(uA[2 * m + 0], cqA2, nmA2);
             const float2 t1 = __ffma2_rn(uA[2 * m + 1], cqA2, nmA2);
-            const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
-            const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
+            const float2 p01 = exp_pair(t0, SAGE_POLY >= 1 && (m & 1) == 0 || SAGE_POLY >= 3);
+            const float2 p23 = exp_pair(t1, false);
             psA = __fadd2_rn(psA, __fadd2_rn(p01, p23));
             const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
-            sts32u(pA + 128u * (uint32_t)m, e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
+#if SAGE_ABL & 64
+            wA = __float_as_uint(f01.x) ^ __float_as_uint(f01.y) ^ __float_as_uint(f23.x) ^ __float_as_uint(f23.y);
+#else
+            wA = e4m3x4_pack(f01.x, f01.y, f23.x, f23.y);
+#endif
           }
           {
             const float2 t0 = __ffma2_rn(uB[2 * m + 0], cqB2, nmB2);
             const float2 t1 = __ffma2_rn(uB[2 * m + 1], cqB2, nmB2);
-            const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
-            const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
+            const float2 p01 = exp_pair(t0, false);
+            const float2 p23 = exp_pair(t1, SAGE_POLY >= 2 && (m & 1) == 1 || SAGE_POLY >= 3);
             psB = __fadd2_rn(psB, __fadd2_rn(p01, p23));
             const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
-            sts32u(pB + 128u * (uint32_t)m, e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
+#if SAGE_ABL & 64
+            wB = __float_as_uint(f01.x) ^ __float_as_uint(f01.y) ^ __float_as_uint(f23.x) ^ __float_as_uint(f23.y);
+#else
+            wB = e4m3x4_pack(f01.x, f01.y, f23.x, f23.y);
+#endif
           }
+#if SAGE_ABL & 1
+          if (wA == 0x12345678u && wB == 0x9abcdef0u) sts32u(pA, wA);   // keeps the values alive
+#elif SAGE_SMEM_PLAIN
+          *reinterpret_cast<uint32_t*>(pA_ptr + 128 * m) = wA;
+          *reinterpret_cast<uint32_t*>(pB_ptr + 128 * m) = wB;
+#else
+          sts32u(pA + 128u * (uint32_t)m, wA);
+          sts32u(pB + 128u * (uint32_t)m, wB);
+#endif
         }
         lA = lA * alphaA + (psA.x + psA.y);                 // this thread's quarter of the row sum
         lB = lB * alphaB + (psB.x + psB.y);
@@ -724,11 +919,10 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t r
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-static uint32_t* g_dbg_ptr = nullptr;
-static int g_dbg_tile = 0;
-static int g_force_tiles_per_cta = 0;
-void set_score_dump(void* ptr, int tile) { g_dbg_ptr = reinterpret_cast<uint32_t*>(ptr); g_dbg_tile = tile; }
-void set_tiles_per_cta(int n) { g_force_tiles_per_cta = (n == 1 || n == 2) ? n : 0; }
+// Test hook: 1 or 2 forces that kernel shape for later launches, 0 leaves the choice to
+// choose_tiles_per_cta.  One relaxed atomic word; launches that race with a change take either value.
+static std::atomic<int> g_force_tiles_per_cta{0};
+void set_tiles_per_cta(int n) { g_force_tiles_per_cta.store((n == 1 || n == 2) ? n : 0, std::memory_order_relaxed); }
 
 template <bool INT8, bool CAUSAL, typename OutT, int NQ>
 static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
@@ -789,8 +983,6 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   ka.Nq = p.Nq; ka.Hq = p.Hq; ka.group = p.Hq / p.H; ka.lse = p.lse; ka.qm = p.qm; ka.D = (int)p.D; ka.vmean = p.vmean;
   ka.o_sb = p.o_strides[0]; ka.o_sh = p.o_strides[1]; ka.o_sr = p.o_strides[2];
   ka.sm_scale = p.sm_scale; ka.status = p.status;
-  ka.dbg = g_dbg_ptr; ka.dbg_tile = g_dbg_tile;
-  // (The score dump indexes by one-tile CTAs, so it keeps that shape.)
   const unsigned q_tiles = (unsigned)((p.Nq + TILE - 1) / TILE);
   static int sm_count[64] = {0};                          // per device, asked once
   int sms = 148, dev = 0;
@@ -800,8 +992,9 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
       sm_count[dev] = 148;
     sms = sm_count[dev];
   }
-  bool two = g_dbg_ptr == nullptr && choose_tiles_per_cta((int64_t)q_tiles, (int64_t)bhq, p.causal != 0, sms) == 2;
-  if (g_force_tiles_per_cta != 0 && g_dbg_ptr == nullptr) two = (g_force_tiles_per_cta == 2);
+  bool two = choose_tiles_per_cta((int64_t)q_tiles, (int64_t)bhq, p.causal != 0, sms) == 2;
+  const int forced = g_force_tiles_per_cta.load(std::memory_order_relaxed);
+  if (forced != 0) two = (forced == 2);
   dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
   cudaError_t e;

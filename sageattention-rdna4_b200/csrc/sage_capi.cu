@@ -136,8 +136,9 @@ int prologue_impl(const void* q, const void* k, const void* v,
   if ((rc = check_strides("q", q_strides)) || (rc = check_strides("k", k_strides)) || (rc = check_strides("v", v_strides)))
     return rc;
   if (!aligned16(q) || !aligned16(k) || !aligned16(v) || !aligned16(q8) || !aligned16(k8) || !aligned16(v8t) ||
-      !aligned16(sk) || !aligned16(svp) || !aligned16(ctrl))
+      !aligned16(sk) || !aligned16(sv) || !aligned16(svp) || !aligned16(ctrl) || !aligned16(vmean))
     return fail(SAGE_E_ARG, "%s: pointers must be 16-byte aligned", who);
+  if (status && (reinterpret_cast<uintptr_t>(status) & 3u)) return fail(SAGE_E_ARG, "%s: status must be 4-byte aligned", who);
   sage::PrologueParams p;
   p.q = q; p.k = k; p.v = v; p.q8 = q8; p.k8 = k8; p.v8t = v8t;
   p.sq = sq; p.sk = sk; p.sv = sv; p.svp = svp; p.s_fold = s_fold; p.mean = mean; p.ctrl = ctrl; p.qm = qm; p.vmean = vmean; p.status = status;
@@ -164,9 +165,13 @@ int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
   if (out_dtype != SAGE_F16 && out_dtype != SAGE_BF16) return fail(SAGE_E_ARG, "%s: bad out_dtype", who);
   if (qk_mode != SAGE_QK_INT8 && qk_mode != SAGE_QK_E4M3) return fail(SAGE_E_ARG, "%s: bad qk_mode", who);
   if ((rc = check_strides("out", o_strides))) return rc;
-  if (!aligned16(q8) || !aligned16(k8) || !aligned16(v8t) || !aligned16(sk) || !aligned16(svp) || !aligned16(out))
+  if (!aligned16(q8) || !aligned16(k8) || !aligned16(v8t) || !aligned16(sk) || !aligned16(svp) || !aligned16(out) ||
+      !aligned16(vmean))
     return fail(SAGE_E_ARG, "%s: pointers must be 16-byte aligned", who);
-  if (!(sm_scale == sm_scale)) return fail(SAGE_E_ARG, "%s: sm_scale is NaN", who);
+  // The kernel takes the row maximum before it multiplies by sm_scale * log2(e) * sq, which keeps
+  // the order only for a positive factor.
+  if (!(sm_scale > 0.f) || !(sm_scale <= 3.0e38f))
+    return fail(SAGE_E_ARG, "%s: sm_scale must be finite and positive (got %g)", who, (double)sm_scale);
   sage::AttnParams p;
   p.q8 = q8; p.k8 = k8; p.v8t = v8t; p.sq = sq; p.sk = sk; p.svp = svp; p.s_fold = s_fold; p.out = out;
   p.lse = lse; p.qm = qm; p.vmean = vmean;
@@ -257,7 +262,7 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
                               int64_t B, int64_t H, int64_t N, int64_t N_pad,
                               const int64_t q_strides[3], const int64_t k_strides[3],
                               const int64_t v_strides[3],
-                              int dtype, int qk_mode, int smooth_k, void* stream) {
+                              int dtype, int qk_mode, int smooth_k, int32_t* status, void* stream) {
   g_err[0] = 0;
   const Dims d = {B, H, H, N, N, sage::HD};
   int rc = check_dims(d);
@@ -272,7 +277,7 @@ int sage_prologue_static_ctrl(const void* q, const void* k, const void* v,
   if (rc) return rc;
   return prologue_impl(q, k, v, q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, nullptr, nullptr, ctrl, d, N_pad,
                        q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream,
-                       "sage_prologue_static_ctrl");
+                       "sage_prologue_static_ctrl", status);
 }
 
 int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* sk,
@@ -296,7 +301,16 @@ int sage_attn_fwd_ex(const void* q8, const float* sq, const void* k8, const floa
                    causal, sm_scale, out_dtype, qk_mode, status, stream, "sage_attn_fwd_ex");
 }
 
-void sage_debug_score_dump(void* ptr, int key_tile) { sage::set_score_dump(ptr, key_tile); }
+int sage_status_mirror(const int32_t* status_dev, int32_t* status_host, void* stream) {
+  g_err[0] = 0;
+  if (!status_dev || !status_host) return fail(SAGE_E_ARG, "sage_status_mirror: null pointer argument");
+  if ((reinterpret_cast<uintptr_t>(status_dev) | reinterpret_cast<uintptr_t>(status_host)) & 3u)
+    return fail(SAGE_E_ARG, "sage_status_mirror: pointers must be 4-byte aligned");
+  cudaError_t e = cudaMemcpyAsync(status_host, status_dev, sizeof(int32_t), cudaMemcpyDeviceToHost,
+                                  reinterpret_cast<cudaStream_t>(stream));
+  if (e != cudaSuccess) return fail(SAGE_E_CUDA, "sage_status_mirror: %s", cudaGetErrorString(e));
+  return SAGE_OK;
+}
 
 void sage_debug_tiles_per_cta(int n) { sage::set_tiles_per_cta(n); }
 

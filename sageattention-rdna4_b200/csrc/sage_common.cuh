@@ -53,15 +53,20 @@ inline cudaError_t launch_after_predecessor(void (*kern)(KArgs...), dim3 grid, d
 }
 #endif
 
-// How many CTAs share one head's sequence in the mean kernel.
-inline int kmean_splits(int64_t bh, int64_t n) {
-  int64_t want = (4 * 148) / bh;                   // one full wave: four resident CTAs on each of 148 SMs
-  int64_t cap = (n + 255) / 256;                   // at least 256 tokens per CTA
+// How many CTAs share one head's sequence in the mean kernel on a device with `sms` SMs: one full
+// wave of four resident CTAs per SM, at least 256 tokens per CTA, at most 64 splits.
+inline int kmean_splits(int64_t bh, int64_t n, int sms) {
+  int64_t want = (4 * (int64_t)sms) / bh;
+  int64_t cap = (n + 255) / 256;
   if (want > cap) want = cap;
   if (want > 64) want = 64;
   if (want < 1) want = 1;
   return (int)want;
 }
+// The scratch for the partial sums is sized without a device at hand, for the largest SM count
+// an sm_100 part has; a launch never uses more splits than that.
+constexpr int KMEAN_SIZING_SMS = 160;
+inline int kmean_splits_max(int64_t bh, int64_t n) { return kmean_splits(bh, n, KMEAN_SIZING_SMS); }
 
 template <typename T> struct Elem;
 template <> struct Elem<__half> {

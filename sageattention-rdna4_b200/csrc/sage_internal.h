@@ -47,8 +47,7 @@ size_t prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
 // Returns cudaSuccess or an error; `why` (if non-null) receives a static description on failure.
 cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** why);
 
-// Debug aid: subsequent attention launches copy the raw score accumulators of one key tile.
-void set_score_dump(void* ptr, int tile);
+// Test hook: force the attention kernel's shape (1 or 2 query tiles per CTA; 0 = automatic).
 void set_tiles_per_cta(int n);
 int choose_tiles_per_cta(int64_t q_tiles, int64_t bhq, bool causal, int sms);
 

@@ -22,6 +22,7 @@
 // for fp16 data when sum|K| < 2^29 per channel and for bf16 data of ordinary dynamic range.
 #include <cuda.h>
 
+#include <algorithm>
 #include <type_traits>
 
 #include "sage_common.cuh"
@@ -531,10 +532,21 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   const int64_t bh = p.B * p.H;
   unsigned* words = reinterpret_cast<unsigned*>(p.ctrl);
   double* partial = reinterpret_cast<double*>(reinterpret_cast<char*>(p.ctrl) + CtrlHeader::partial_off(bh));
-  cudaError_t e = cudaMemsetAsync(p.ctrl, 0, CtrlHeader::words(bh) * 4, st);
+  // SM count and the opt-in to 64 KB of dynamic shared memory: looked up once per device
+  static int sm_count[64] = {0};
+  static bool opted_in[64][2] = {{false}};
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
+  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
+  if (sm_count[dev] == 0) {
+    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess) return e;
+  }
+  e = cudaMemsetAsync(p.ctrl, 0, CtrlHeader::words(bh) * 4, st);
+  if (e != cudaSuccess) return e;
+  const int nsplit = std::min(kmean_splits(bh, p.N, sm_count[dev]), kmean_splits_max(bh, p.N));
   if (p.smooth_k) {
-    const int nsplit = kmean_splits(bh, p.N);
     long long chunk = (p.N + nsplit - 1) / nsplit;
     chunk = (chunk + 15) / 16 * 16;
     dim3 grid(nsplit, (unsigned)bh);
@@ -545,7 +557,6 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     if (e != cudaSuccess) return e;
   }
   if (p.vmean) {
-    const int nsplit = kmean_splits(bh, p.N);
     long long chunk = (p.N + nsplit - 1) / nsplit;
     chunk = (chunk + 15) / 16 * 16;
     dim3 grid(nsplit, (unsigned)bh);
@@ -574,17 +585,6 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
       !make_map4(&mk, p.k, dt, p.D, p.N, p.H, p.B, p.k_strides) ||
       !make_map4(&mv, p.v, dt, p.D, p.N, p.H, p.B, p.v_strides))
     return cudaErrorInvalidValue;
-  // SM count and the opt-in to 64 KB of dynamic shared memory: looked up once per device
-  static int sm_count[64] = {0};
-  static bool opted_in[64][2] = {{false}};
-  int dev = 0;
-  e = cudaGetDevice(&dev);
-  if (e != cudaSuccess) return e;
-  if (dev < 0 || dev >= 64) return cudaErrorInvalidDevice;
-  if (sm_count[dev] == 0) {
-    e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
-    if (e != cudaSuccess) return e;
-  }
   const long long total = 2 * (long long)bh * tk + (long long)a.BHq * tq;
   long long ctas = (long long)sm_count[dev] * QT_MINBLOCKS;
   if (ctas > total) ctas = total;
@@ -603,7 +603,7 @@ cudaError_t launch_prologue(const PrologueParams& p, cudaStream_t st) {
 
 size_t prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N) {
   const int64_t bh = B * H;
-  return CtrlHeader::partial_off(bh) + (size_t)bh * kmean_splits(bh, N) * HD * sizeof(double);
+  return CtrlHeader::partial_off(bh) + (size_t)bh * kmean_splits_max(bh, N) * HD * sizeof(double);
 }
 
 }  // namespace sage

@@ -34,7 +34,7 @@ SIGNATURES = {
     "sage_prologue_static_ctrl_capacity": (ctypes.c_size_t, []),
     "sage_prologue_static_ctrl": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P,
                                                  _I64, _I64, _I64, _I64, _S3, _S3, _S3,
-                                                 ctypes.c_int, ctypes.c_int, ctypes.c_int, _P]),
+                                                 ctypes.c_int, ctypes.c_int, ctypes.c_int, _P, _P]),
     "sage_attn_fwd": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, _P,
                                      _I64, _I64, _I64, _I64, _S3,
                                      ctypes.c_int, ctypes.c_float, ctypes.c_int, ctypes.c_int, _P, _P]),
@@ -49,7 +49,7 @@ SIGNATURES = {
     "sage_attention_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, ctypes.c_size_t, _I64, _I64, _I64, _I64, _I64, _I64,
                                          _S3, _S3, _S3, _S3, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_int, ctypes.c_int, ctypes.c_float, _P]),
-    "sage_debug_score_dump": (None, [_P, ctypes.c_int]),
+    "sage_status_mirror": (ctypes.c_int, [_P, _P, _P]),
     "sage_debug_tiles_per_cta": (None, [ctypes.c_int]),
     "sage_attention_tiles_per_cta": (ctypes.c_int, [_I64, _I64, _I64, ctypes.c_int, ctypes.c_int]),
     "sage_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64]),

@@ -12,6 +12,7 @@ codes are materialised, keys are padded to 128, and the fold S is computed insid
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from collections import OrderedDict
 from typing import Dict, Optional, Tuple
@@ -44,21 +45,26 @@ def strided_view_reason(t: torch.Tensor) -> Optional[str]:
     stride[k+1] >= stride[k]*size[k]); strides below 2**39 elements (the reference: 2**31)."""
     if t.dim() != 4:
         return "rank"
-    if int(t.stride(3)) != 1:
+    strides = tuple(int(x) for x in t.stride())
+    extents = tuple(int(x) for x in t.shape)
+    if strides[3] != 1:
         return "stride_last"
-    st = [int(s) for s in t.stride()]
-    if any(s <= 0 for s in st):
+    if min(strides) <= 0:
         return "stride_nonpos"
-    if any(st[i] % 8 for i in (0, 1, 2)):
+    if any(x % 8 for x in strides[:3]):
         return "stride_align"
-    if int(t.data_ptr()) % 16:
+    if t.data_ptr() % 16:
         return "ptr_align"
-    sh = [int(x) for x in t.shape]
-    dims = sorted((st[i], sh[i]) for i in range(4) if sh[i] > 1)
-    for (s0, n0), (s1, _n1) in zip(dims, dims[1:]):
-        if s1 < s0 * n0:
+    # Walk the axes that have more than one element from the smallest stride up: each must step
+    # over everything the axes below it can reach, or two index tuples share an address.
+    reach = 0
+    for stride, extent in sorted(zip(strides, extents)):
+        if extent <= 1:
+            continue
+        if stride < reach:
             return "stride_overlap"
-    if any(s > _STRIDE_MAX for s in st):
+        reach = stride * extent
+    if max(strides) > _STRIDE_MAX:
         return "stride_range"
     return None
 
@@ -210,35 +216,118 @@ def attn_launch(pq: Dict[str, torch.Tensor], out: torch.Tensor, is_causal: bool,
 
 
 # ---- the whole call ------------------------------------------------------------------------------
+# Device-side failures.  Every wait inside the kernels is bounded; a wait that runs out leaves a
+# code in the call's status word (a word of the workspace) and the output of that call is
+# undefined.  The reference raises in such a case only in its strict mode and otherwise falls back
+# (sageattention/sk1_backend/__init__.py:1022-1027,1114-1123); this path has no fallback, so the
+# failure must reach the caller.  After every call a 4-byte copy of the status word into pinned
+# host memory is enqueued behind it (no synchronisation); the next call on that stream, `check()`
+# or `status()` looks at the host word and raises RuntimeError when it is non-zero.
+# SAGEATTN_B200_STRICT=1 synchronises after every call and checks at once;
+# SAGEATTN_B200_WATCH=0 switches the copy off.
+STATUS_BITS = ((1, "the TMA producer of the attention kernel"), (2, "the MMA issuer of the attention kernel"),
+               (4, "a softmax warp of the attention kernel"), (0x100, "a tile load of the quantisation prologue"))
+
+
+def describe_status(code: int) -> str:
+    who = [name for bit, name in STATUS_BITS if code & bit]
+    return "status 0x%x: a bounded wait ran out in %s; the output of that call is undefined" % (
+        code & 0xFFFFFFFF, " and ".join(who) if who else "an unknown role")
+
+
+def _env_flag(name: str, default: bool) -> bool:
+    v = os.environ.get(name)
+    if v is None or v == "":
+        return default
+    return v.strip().lower() not in ("0", "false", "off", "no")
+
+
+class _StreamState:
+    """What the path keeps per (device, stream): one grow-only workspace (intermediates of a call
+    live only until its attention kernel has run, and calls on one stream are ordered) and the
+    pinned host word that mirrors the status word of the most recent call."""
+
+    __slots__ = ("ws", "host", "host_word", "status_off", "shape")
+
+    def __init__(self, host_word=None):
+        self.ws = None
+        self.host = None                    # pinned tensor that owns the memory behind host_word
+        self.host_word = host_word          # ctypes.c_int32 view of it (tests pass a plain c_int32)
+        self.status_off = None
+        self.shape = None
+
+    def pending(self) -> int:
+        return 0 if self.host_word is None else int(self.host_word.value)
+
+    def raise_if_failed(self, where: str):
+        code = self.pending()
+        if code:
+            self.host_word.value = 0
+            raise RuntimeError("sageattn (B200 path), reported at %s: %s" % (where, describe_status(code)))
+
+
+_STRICT = _env_flag("SAGEATTN_B200_STRICT", False)
+_WATCH = _env_flag("SAGEATTN_B200_WATCH", True) or _STRICT
+
 _ws_lock = threading.Lock()
-_ws_cache: "OrderedDict[Tuple, torch.Tensor]" = OrderedDict()
-_WS_CACHE_ENTRIES = 4
+_states: "OrderedDict[Tuple[int, int], _StreamState]" = OrderedDict()
+_STATE_ENTRIES = 8
+_WS_GRANULE = 1 << 20
+
+
+def _state(dev, stream_id: int, create: bool = True) -> Optional[_StreamState]:
+    key = (dev.index, int(stream_id))
+    with _ws_lock:
+        st = _states.get(key)
+        if st is not None:
+            _states.move_to_end(key)
+            return st
+        if not create:
+            return None
+        st = _states[key] = _StreamState()
+        while len(_states) > _STATE_ENTRIES:
+            _states.popitem(last=False)
+    return st
 
 
 def _workspace(dev, stream_id: int, b: int, h: int, n: int, hkv: Optional[int] = None,
                nk: Optional[int] = None) -> torch.Tensor:
-    """A cached workspace per (device, stream, shape): intermediates of one call live only until
-    the attention kernel of that call has run, and calls on one stream are ordered."""
+    """The workspace of (device, stream), grown if this shape needs more than it holds."""
     hkv = h if hkv is None else hkv
     nk = n if nk is None else nk
-    key = (dev.index, stream_id, b, h, hkv, n, nk)
-    with _ws_lock:
-        ws = _ws_cache.get(key)
-        if ws is not None:
-            _ws_cache.move_to_end(key)
-            return ws
     nbytes = _native.load().sage_workspace_bytes_ex(b, h, hkv, n, nk)
-    ws = torch.empty((nbytes,), dtype=torch.uint8, device=dev)
-    with _ws_lock:
-        _ws_cache[key] = ws
-        while len(_ws_cache) > _WS_CACHE_ENTRIES:
-            _ws_cache.popitem(last=False)
-    return ws
+    return _grow(_state(dev, stream_id), dev, nbytes)
+
+
+def _grow(st: _StreamState, dev, nbytes: int) -> torch.Tensor:
+    if st.ws is None or st.ws.numel() < nbytes:
+        st.ws = None                         # release first: the two need not be resident together
+        st.ws = torch.empty(((nbytes + _WS_GRANULE - 1) // _WS_GRANULE * _WS_GRANULE,), dtype=torch.uint8, device=dev)
+    return st.ws
+
+
+def _host_word(st: _StreamState):
+    if st.host_word is None:
+        st.host = torch.zeros((1,), dtype=torch.int32).pin_memory()
+        st.host_word = ctypes.c_int32.from_address(st.host.data_ptr())
+    return st.host_word
 
 
 def clear_workspaces():
     with _ws_lock:
-        _ws_cache.clear()
+        _states.clear()
+
+
+def check(device=None):
+    """Wait for the current stream of `device` and raise RuntimeError if a call on it reported a
+    device-side failure (see STATUS_BITS)."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else torch.device(device)
+    stream = torch.cuda.current_stream(dev)
+    st = _state(dev, stream.cuda_stream, create=False)
+    if st is None:
+        return
+    stream.synchronize()
+    st.raise_if_failed("check()")
 
 
 # Calls repeat with the same shapes and strides (a diffusion transformer issues the same attention
@@ -256,9 +345,9 @@ def _logical_strides(t: torch.Tensor, nhd: bool):
 
 
 def _validated(q, k, v, tensor_layout):
-    """(b, hq, hkv, nq, nk, d, nhd, stride triples of q, k, v and of a fresh output, dtype code) for
-    a call inside the envelope; raises the documented exception otherwise.  Pointer alignment is
-    part of the signature."""
+    """(b, hq, hkv, nq, nk, d, nhd, stride triples of q, k, v and of a fresh output, dtype code,
+    workspace bytes, offset of the status word in the workspace) for a call inside the envelope;
+    raises the documented exception otherwise.  Pointer alignment is part of the signature."""
     key = (tensor_layout, q.shape, q.stride(), k.shape, k.stride(), v.shape, v.stride(), q.dtype, k.dtype,
            v.dtype, q.device, k.device, v.device,
            (q.data_ptr() | k.data_ptr() | v.data_ptr()) & 15)
@@ -284,9 +373,14 @@ def _validated(q, k, v, tensor_layout):
     b, hq, hkv, nq, nk, d = int(b), int(hq), int(hkv), int(nq), int(nk), int(d)
     # (batch, head, row) strides of a freshly allocated output with q's shape
     o3 = _native.strides3(nq * hq * d, d, hq * d) if nhd else _native.strides3(hq * nq * d, nq * d, d)
+    lib = _native.load()
+    offs = (ctypes.c_size_t * 13)()
+    if lib.sage_workspace_layout_ex(b, hq, hkv, nq, nk, offs) != 13:
+        raise _native.SageNativeError("sage_workspace_layout_ex failed")
     val = (b, hq, hkv, nq, nk, d, nhd,
            _native.strides3(*_logical_strides(q, nhd)), _native.strides3(*_logical_strides(k, nhd)),
-           _native.strides3(*_logical_strides(v, nhd)), o3, _dtype_code(q.dtype))
+           _native.strides3(*_logical_strides(v, nhd)), o3, _dtype_code(q.dtype),
+           int(lib.sage_workspace_bytes_ex(b, hq, hkv, nq, nk)), int(offs[10]))
     if len(_sig_cache) >= _SIG_CACHE_ENTRIES:
         _sig_cache.clear()
     _sig_cache[key] = val
@@ -301,9 +395,12 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     (B, Hq, Nq).  `smooth_v` quantises V minus its sequence mean and adds the mean back to the
     output.  Raises ValueError for a call outside the envelope."""
     _counters["calls"] += 1
-    b, h, hkv, n, nk, d, nhd, q3, k3, v3, o3, dt = _validated(q, k, v, tensor_layout)
+    b, h, hkv, n, nk, d, nhd, q3, k3, v3, o3, dt, ws_bytes, status_off = _validated(q, k, v, tensor_layout)
     if is_causal and nk != n:
         raise ValueError("sageattn (B200 path): a causal call needs q_len == kv_len")
+    scale = d ** -0.5 if sm_scale is None else float(sm_scale)
+    if not (0.0 < scale < float("inf")):
+        raise ValueError("sageattn (B200 path): sm_scale must be finite and positive, got %r" % (sm_scale,))
     lib = _native.load()
     dev = q.device
     if out is None:
@@ -320,19 +417,33 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     else:
         qk_mode = _native.SAGE_QK_INT8 if int8 else _native.SAGE_QK_E4M3
     stream_id = torch.cuda.current_stream(dev).cuda_stream
-    ws = _workspace(dev, stream_id, b, h, n, hkv, nk)
+    st = _state(dev, stream_id)
+    if st.host_word is not None and st.host_word.value:
+        st.raise_if_failed("the next call on the stream")        # an earlier call's failure, seen without a sync
+    ws = st.ws
+    if ws is None or ws.numel() < ws_bytes:
+        ws = _grow(st, dev, ws_bytes)
+    st.status_off, st.shape = status_off, (b, h, hkv, n, nk)
     lse = torch.empty((b, h, n), dtype=torch.float32, device=dev) if return_lse else None
+    ws_ptr = ws.data_ptr()
     args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 0 if lse is None else lse.data_ptr(),
-            ws.data_ptr(), ws.numel(), b, h, hkv, n, nk, d, q3, k3, v3, o3, dt, qk_mode,
-            1 if is_causal else 0, 1 if smooth_k else 0, 1 if smooth_v else 0,
-            d ** -0.5 if sm_scale is None else float(sm_scale), stream_id)
+            ws_ptr, ws.numel(), b, h, hkv, n, nk, d, q3, k3, v3, o3, dt, qk_mode,
+            1 if is_causal else 0, 1 if smooth_k else 0, 1 if smooth_v else 0, scale, stream_id)
+    watch = _WATCH
     if torch.cuda.current_device() == dev.index:
         rc = lib.sage_attention_ex(*args)
+        if watch and not rc:
+            rc = lib.sage_status_mirror(ws_ptr + status_off, ctypes.addressof(_host_word(st)), stream_id)
     else:
         with torch.cuda.device(dev):
             rc = lib.sage_attention_ex(*args)
+            if watch and not rc:
+                rc = lib.sage_status_mirror(ws_ptr + status_off, ctypes.addressof(_host_word(st)), stream_id)
     if rc:
         _native.check(rc, "sage_attention_ex")
+    if _STRICT:
+        torch.cuda.current_stream(dev).synchronize()
+        st.raise_if_failed("this call (strict mode)")
     if return_lse:
         return out, lse
     return out
@@ -364,21 +475,30 @@ def workspace_views(b: int, h: int, n: int, ws: torch.Tensor, int8: bool) -> Dic
 
 def last_status(q_like: torch.Tensor, b: int, h: int, n: int, hkv: Optional[int] = None,
                 nk: Optional[int] = None) -> int:
-    """Status word of the most recent call of that shape on the current stream (synchronises)."""
+    """Status word of the most recent `sage_call` on the current stream of q_like's device, read
+    from that call's workspace (synchronises).  The shape must be that call's shape; raises
+    RuntimeError if no call has run on the stream or the last one had another shape."""
     dev = q_like.device
-    ws = _workspace(dev, int(torch.cuda.current_stream(dev).cuda_stream), b, h, n, hkv, nk)
-    lib = _native.load()
-    offs = (ctypes.c_size_t * 13)()
-    if lib.sage_workspace_layout_ex(b, h, h if hkv is None else hkv, n, n if nk is None else nk, offs) != 13:
-        raise _native.SageNativeError("sage_workspace_layout_ex failed")
-    return int(ws[offs[10]: offs[10] + 4].view(torch.int32).item())
+    stream = torch.cuda.current_stream(dev)
+    st = _state(dev, stream.cuda_stream, create=False)
+    want = (b, h, h if hkv is None else hkv, n, n if nk is None else nk)
+    if st is None or st.ws is None or st.shape is None:
+        raise RuntimeError("last_status: no call has run on this stream")
+    if st.shape != want:
+        raise RuntimeError("last_status: the last call on this stream had shape %r, not %r" % (st.shape, want))
+    stream.synchronize()
+    return int(st.ws[st.status_off: st.status_off + 4].view(torch.int32).item())
 
 
 def status() -> dict:
     """Small status record in the spirit of the reference's int8_status()/bf16_status()
-    (sageattention/sk1_backend/__init__.py:529-558)."""
+    (sageattention/sk1_backend/__init__.py:529-558).  `device_status` lists the non-zero status
+    words already copied back from finished calls, per (device, stream); nothing is synchronised."""
     info = dict(library=_native.LIB_PATH, loaded=_native._lib is not None, calls=_counters["calls"],
-                refusals=_counters["refusals"], arch="sm_100a", tile=TILE, head_dim=HEAD_DIM)
+                refusals=_counters["refusals"], arch="sm_100a", tile=TILE, head_dim=HEAD_DIM,
+                strict=_STRICT, watch=_WATCH)
+    with _ws_lock:
+        info["device_status"] = {key: st.pending() for key, st in _states.items() if st.pending()}
     try:
         info["version"] = _native.load().sage_version()
     except _native.SageNativeError as exc:

@@ -120,3 +120,53 @@ def test_attention_shape_rule_is_host_arithmetic():
     assert f(0, 128) == 0 and f(4, 0) == 0 and f(4, 128, sms=0) == 0
     # more SMs move the thresholds with them
     assert f(48, 1024, sms=96) == 2 and f(48, 1024, sms=192) == 2
+
+
+def test_vector_accessed_pointers_must_be_aligned():
+    """Every pointer the kernels touch with 16-byte accesses is checked on the host: a pointer that
+    is only 4-byte aligned is refused before any launch (so these calls cannot fault a device)."""
+    lib = _native.load()
+    s3 = _native.strides3(1024, 512, 128)
+    buf = (ctypes.c_char * 8192)()
+    base = (ctypes.addressof(buf) + 255) // 256 * 256
+    ok, off = ctypes.c_void_p(base), ctypes.c_void_p(base + 4)
+
+    def prologue(**bad):
+        names = ["q", "k", "v", "q8", "sq", "k8", "sk", "v8t", "sv", "svp", "s_fold", "mean", "qm", "vmean", "ctrl"]
+        args = [bad.get(n, ok) for n in names]
+        return lib.sage_prologue_ex(*args, 1, 2, 2, 16, 16, 128, 128, s3, s3, s3, 0, 0, 1, None)
+
+    for name in ("q", "k", "v", "q8", "k8", "v8t", "sk", "sv", "svp", "vmean", "ctrl"):
+        assert prologue(**{name: off}) == _native.SAGE_E_ARG, name
+        assert b"16-byte aligned" in lib.sage_last_error(), name
+
+    def attn(**bad):
+        names = ["q8", "sq", "k8", "sk", "v8t", "svp", "s_fold", "out", "lse", "qm", "vmean"]
+        args = [bad.get(n, ok) for n in names]
+        return lib.sage_attn_fwd_ex(*args, 1, 2, 2, 16, 16, 128, 128, s3, 0, 0.1, 0, 0, ok, None)
+
+    for name in ("q8", "k8", "v8t", "sk", "svp", "out", "vmean"):
+        assert attn(**{name: off}) == _native.SAGE_E_ARG, name
+        assert b"16-byte aligned" in lib.sage_last_error(), name
+
+
+@pytest.mark.parametrize("scale", [0.0, -0.1, float("inf"), float("-inf"), float("nan")])
+def test_sm_scale_must_be_finite_and_positive(scale):
+    lib = _native.load()
+    s3 = _native.strides3(1024, 512, 128)
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.c_void_p((ctypes.addressof(buf) + 255) // 256 * 256)
+    rc = lib.sage_attn_fwd(*([p] * 8), 1, 2, 16, 128, s3, 0, scale, 0, 0, p, None)
+    assert rc == _native.SAGE_E_ARG
+    assert b"sm_scale" in lib.sage_last_error()
+
+
+def test_static_scratch_entry_point_checks_its_status_pointer():
+    lib = _native.load()
+    s3 = _native.strides3(1024, 512, 128)
+    buf = (ctypes.c_char * 4096)()
+    base = (ctypes.addressof(buf) + 255) // 256 * 256
+    # shape too large for the built-in scratch: refused before the status pointer is even looked at
+    rc = lib.sage_prologue_static_ctrl(*([ctypes.c_void_p(base)] * 12), 32, 64, 65536, 65536, s3, s3, s3, 0, 0, 1,
+                                       ctypes.c_void_p(base + 2), None)
+    assert rc == _native.SAGE_E_UNSUPPORTED

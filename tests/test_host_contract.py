@@ -150,3 +150,37 @@ def test_environment_switches_are_read_at_import():
     assert fp8.stdout.split()[:2] == ["False", "True"] and "no CPU path" in fp8.stderr
     default = run({"SAGEATTN_SK1_INT8": "", "SAGEATTN_SK1_BACKEND": ""})
     assert default.stdout.split()[:2] == ["True", "True"] and "no CPU path" in default.stderr
+
+
+def test_device_status_codes_become_exceptions():
+    """A status word that a finished call left non-zero is turned into RuntimeError by the host
+    logic (the word is faked here; no GPU involved) and cleared, so that the report is made once."""
+    import ctypes
+    word = ctypes.c_int32(0)
+    st = be._StreamState(host_word=word)
+    st.raise_if_failed("test")                                   # zero: nothing happens
+    assert st.pending() == 0
+    word.value = 2
+    with pytest.raises(RuntimeError, match="MMA issuer"):
+        st.raise_if_failed("test")
+    assert word.value == 0 and st.pending() == 0
+    word.value = 0x100 | 4
+    with pytest.raises(RuntimeError) as exc:
+        st.raise_if_failed("the next call on the stream")
+    msg = str(exc.value)
+    assert "0x104" in msg and "softmax warp" in msg and "prologue" in msg and "undefined" in msg
+    assert "unknown role" in be.describe_status(0x40)
+    assert be.status()["watch"] in (True, False) and "device_status" in be.status()
+
+
+def test_strict_and_watch_switches_are_read_from_the_environment():
+    import subprocess
+    import sys
+    code = ("import sys; sys.path.insert(0, %r); from sageattention import b200_backend as be; "
+            "print(int(be._STRICT), int(be._WATCH))" % os.path.dirname(os.path.dirname(be.__file__)))
+    run = lambda env: subprocess.run([sys.executable, "-c", code], env={**os.environ, **env}, capture_output=True,
+                                     text=True, check=True).stdout.split()
+    assert run({"SAGEATTN_B200_STRICT": "", "SAGEATTN_B200_WATCH": ""}) == ["0", "1"]
+    assert run({"SAGEATTN_B200_STRICT": "1", "SAGEATTN_B200_WATCH": "0"}) == ["1", "1"]     # strict needs the copy
+    assert run({"SAGEATTN_B200_STRICT": "0", "SAGEATTN_B200_WATCH": "0"}) == ["0", "0"]
+

@@ -81,3 +81,14 @@ def test_sharded_call_and_gather(world, units):
                 p.terminate()
             assert p.exitcode == 0
         assert all(ret.get(r) for r in range(world))
+
+
+def test_scaling_configuration_partition():
+    """The 192 (batch, head) units of the B=4, H=48 scaling configuration split evenly over
+    1, 2, 4 and 8 ranks: 192 / 96 / 48 / 24 units each, contiguous, covering every unit once."""
+    from sageattention.sharding import partition_units
+    for world, per in ((1, 192), (2, 96), (4, 48), (8, 24)):
+        ranges = [partition_units(192, world, r) for r in range(world)]
+        assert all(hi - lo == per for lo, hi in ranges)
+        assert ranges[0][0] == 0 and ranges[-1][1] == 192
+        assert all(a[1] == b[0] for a, b in zip(ranges, ranges[1:]))

@@ -38,7 +38,7 @@ def _buffers(b, h, n, dev):
                 mean=torch.full((bh, 128), -7.0, **f32))
 
 
-def _call_static(lib, q, k, v, o, smooth, int8):
+def _call_static(lib, q, k, v, o, smooth, int8, status=None):
     b, h, n, _ = q.shape
     p = lambda t: ctypes.c_void_p(int(t.data_ptr()))
     s3 = lambda t: _native.strides3(t.stride(0), t.stride(1), t.stride(2))
@@ -46,7 +46,8 @@ def _call_static(lib, q, k, v, o, smooth, int8):
     return lib.sage_prologue_static_ctrl(
         p(q), p(k), p(v), p(o["q8"]), p(o["sq"]), p(o["k8"]), p(o["sk"]), p(o["v8t"]), p(o["sv"]),
         p(o["svp"]), p(o["S"]), p(o["mean"]), b, h, n, be.pad_len(n), s3(q), s3(k), s3(v),
-        0 if q.dtype == torch.float16 else 1, 0 if int8 else 1, 1 if smooth else 0, stream)
+        0 if q.dtype == torch.float16 else 1, 0 if int8 else 1, 1 if smooth else 0,
+        None if status is None else p(status), stream)
 
 
 def test_static_scratch_matches_caller_scratch_twice_in_a_row():
@@ -58,18 +59,34 @@ def test_static_scratch_matches_caller_scratch_twice_in_a_row():
         (1, 6, 1000, torch.float16, True, 11),     # int8 codes, mean on, a |V| > 448 token
         (2, 3, 333, torch.bfloat16, True, 12),     # e4m3 codes, different shape: stale scratch contents
     ]
-    for b, h, n, dtype, smooth, seed in cases:
+    # The caller cannot look inside the built-in scratch, so a wait that ran out is reported in a
+    # word of the caller's own: it must stay zero.
+    status = torch.zeros(1, dtype=torch.int32, device=dev)
+    for i, (b, h, n, dtype, smooth, seed) in enumerate(cases):
         q, k, v = R.make_inputs(b, h, n, 128, dtype, seed=seed, k_bias_std=1.0, device=dev)
         v[0, 1, 5] = 20000.0
         int8 = dtype == torch.float16
         want = be.quant_qkv(q, k, v, smooth_k=smooth, int8=int8)        # sage_prologue, caller-owned scratch
         got = _buffers(b, h, n, dev)
-        rc = _call_static(lib, q, k, v, got, smooth, int8)
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info(dev)[0]
+        rc = _call_static(lib, q, k, v, got, smooth, int8, status)
         assert rc == 0, lib.sage_last_error()
         torch.cuda.synchronize()
+        if i > 0:
+            # "allocates nothing", observed from outside: once the first call on the device has
+            # resolved the array's address, a call leaves the device's free memory as it found it
+            assert torch.cuda.mem_get_info(dev)[0] == free_before
         for key in KEYS:
             assert bytes_equal(got[key], want[key].view(got[key].dtype)), (key, b, h, n)
         assert want["S"].max().item() > 1.0
+        assert status.item() == 0
+    # and without a status word, as before
+    got = _buffers(b, h, n, dev)
+    assert _call_static(lib, q, k, v, got, smooth, int8, None) == 0, lib.sage_last_error()
+    torch.cuda.synchronize()
+    for key in KEYS:
+        assert bytes_equal(got[key], want[key].view(got[key].dtype)), key
 
 
 def test_oversized_shape_is_refused_before_any_launch():
@@ -80,6 +97,6 @@ def test_oversized_shape_is_refused_before_any_launch():
     p = ctypes.c_void_p(int(dummy.data_ptr()))
     s3 = _native.strides3(h * n * 128, n * 128, 128)
     rc = lib.sage_prologue_static_ctrl(p, p, p, p, p, p, p, p, p, p, p, p, b, h, n, be.pad_len(n),
-                                       s3, s3, s3, 0, 0, 1, None)
+                                       s3, s3, s3, 0, 0, 1, None, None)
     assert rc == _native.SAGE_E_UNSUPPORTED
     assert b"control scratch" in lib.sage_last_error()
