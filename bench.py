@@ -87,7 +87,8 @@ def peaks() -> dict:
 class ClockSampler:
     """Samples SM clock and throttle reasons through NVML (read-only) during the timed region."""
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period: float = 0.05):
+        self.period = period
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self._stop = threading.Event()
         self._thread = None
@@ -117,7 +118,7 @@ class ClockSampler:
                         self.reasons.add(name)
             except Exception:
                 pass
-            self._stop.wait(0.05)
+            self._stop.wait(self.period)
 
     def __enter__(self):
         if self._nv is not None:
@@ -164,9 +165,12 @@ def bind_near_gpu(phys_index: int) -> str:
         return "unchanged (%s)" % type(exc).__name__
 
 
+OUTLIER_FRAC = 0.001
+
+
 def make_workload(dtype=torch.float16):
     from oracle import ref_numerics as R   # input generator only; nothing of the oracle is timed here
-    return R.make_inputs(B, H, N, D, dtype, seed=SEED, outlier_frac=0.001)
+    return R.make_inputs(B, H, N, D, dtype, seed=SEED, outlier_frac=OUTLIER_FRAC)
 
 
 def cpu_baseline(causal: bool, rows: int = 0) -> dict:
@@ -202,43 +206,53 @@ def measure_8bit_peaks(dev, phys_index: int, sustain_s: float = 4.0) -> dict:
     fl = 2.0 * n ** 3
     res = {"shape": "8192^3", "how": "burst = best of 10 launches (CUDA events); sustained = back to back for ~%.0f s" % sustain_s}
 
-    def rate(name, fn):
+    def burst(name, fn):
         try:
             for _ in range(3):
                 fn()
             torch.cuda.synchronize(dev)
+            time.sleep(1.0)                            # from an idle, cool GPU
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             best = float("inf")
-            with ClockSampler(phys_index) as c0:
+            with ClockSampler(phys_index, period=0.002) as c0:
                 for _ in range(10):
                     a.record()
                     fn()
                     b.record()
                     torch.cuda.synchronize(dev)
                     best = min(best, a.elapsed_time(b))
-            iters = max(10, int(sustain_s * 1e3 / best))
-            with ClockSampler(phys_index) as c1:
-                a.record()
-                for _ in range(iters):
-                    fn()
-                b.record()
-                torch.cuda.synchronize(dev)
-            sus = a.elapsed_time(b) / iters
-            res[name] = dict(burst_tflops=fl / (best * 1e-3) / 1e12, sustained_tflops=fl / (sus * 1e-3) / 1e12,
-                             burst_sm_mhz=c0.summary()["sm_mhz"], sustained_sm_mhz=c1.summary()["sm_mhz"],
-                             sustained_reasons=c1.summary()["reasons"], sustained_iters=iters)
+            res[name] = dict(burst_tflops=fl / (best * 1e-3) / 1e12, burst_ms=best, burst_sm_mhz=c0.summary()["sm_mhz"])
         except Exception as exc:                       # the library refused the call: say so, measure the rest
             res[name] = dict(error="%s: %s" % (type(exc).__name__, str(exc)[:200]))
 
+    def sustained(name, fn):
+        if "error" in res.get(name, {}):
+            return
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        iters = max(10, int(sustain_s * 1e3 / res[name]["burst_ms"]))
+        with ClockSampler(phys_index) as c1:
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize(dev)
+        sus = a.elapsed_time(b) / iters
+        res[name].update(sustained_tflops=fl / (sus * 1e-3) / 1e12, sustained_sm_mhz=c1.summary()["sm_mhz"],
+                         sustained_reasons=c1.summary()["reasons"], sustained_iters=iters)
+
     a8 = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev)
     b8 = torch.randint(-127, 128, (n, n), dtype=torch.int8, device=dev).t()      # column-major operand
-    rate("int8", lambda: torch._int_mm(a8, b8))
-    del a8, b8
     af = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn)
     bf = torch.randn(n, n, device=dev).to(torch.float8_e4m3fn).t()
     one = torch.ones((), dtype=torch.float32, device=dev)
-    rate("e4m3", lambda: torch._scaled_mm(af, bf, scale_a=one, scale_b=one, out_dtype=torch.bfloat16))
-    del af, bf
+    f_i8 = lambda: torch._int_mm(a8, b8)
+    f_f8 = lambda: torch._scaled_mm(af, bf, scale_a=one, scale_b=one, out_dtype=torch.bfloat16)
+    burst("int8", f_i8)                                # both bursts before either long loop heats the part
+    burst("e4m3", f_f8)
+    sustained("int8", f_i8)
+    time.sleep(1.0)
+    sustained("e4m3", f_f8)
+    del a8, b8, af, bf
     return res
 
 
@@ -321,6 +335,26 @@ def other_arms(q, k, v, dev, causal_main: bool) -> dict:
         return a.elapsed_time(b) / iters
 
     out = {}
+    # The headline inputs have 0.1 % dominant keys, on which the attention kernel's negligible-tile
+    # fast path skips the exponentials of most key tiles.  Two lines put that in the open: the
+    # same call with the path switched off (every tile exponentiated, as the reference does), and
+    # the same shape on inputs without dominant keys (nothing to skip).
+    from sageattention import _native
+    lib = _native.load()
+    lib.sage_debug_skip_threshold(0.0)
+    try:
+        ms = timed(lambda: sageattention.sageattn(q, k, v, is_causal=causal_main), 3)
+    finally:
+        lib.sage_debug_skip_threshold(-1.0)
+    out["headline_fast_path_off"] = dict(ms=ms, tflops=flops(causal_main) / (ms * 1e-3) / 1e12)
+    gen = torch.Generator(device=dev).manual_seed(SEED)
+    kd = torch.randn(k.shape, generator=gen, device=dev, dtype=torch.float32).to(k.dtype)
+    from sageattention import b200_backend as be
+    be.reset_adaptive()          # same shape, other data: what the headline calls taught does not apply
+    ms = timed(lambda: sageattention.sageattn(q, kd, v, is_causal=causal_main), 3)
+    out["headline_shape_without_dominant_keys"] = dict(ms=ms, tflops=flops(causal_main) / (ms * 1e-3) / 1e12)
+    del kd
+    be.reset_adaptive()
     ms = timed(lambda: sageattention.sageattn(q, k, v, is_causal=not causal_main), 3)
     out["fp16_%s" % ("causal" if not causal_main else "non_causal")] = dict(
         ms=ms, tflops=flops(not causal_main) / (ms * 1e-3) / 1e12)
@@ -458,8 +492,9 @@ def run_reference(args) -> int:
 
 
 def workload_config(causal: bool, gpus: int) -> dict:
-    return dict(workload="video-length attention B=%d(per GPU) H=%d N=%d D=%d fp16 %s smooth_k, 0.1%% K tokens x50"
-                % (B, H, N, D, "causal" if causal else "non-causal"),
+    return dict(workload="video-length attention B=%d(per GPU) H=%d N=%d D=%d fp16 %s smooth_k, %s"
+                % (B, H, N, D, "causal" if causal else "non-causal",
+                   "0.1% K tokens x50" if OUTLIER_FRAC else "no dominant keys (profiling aid)"),
                 global_batch=B * gpus, heads=H, seq_len=N, head_dim=D, causal=causal, seed=SEED,
                 sharding="batch x head units across GPUs, no collective" if gpus > 1 else "single GPU",
                 l2="inputs (3 x 584 MB) exceed the 126 MB L2; no explicit flush")
@@ -477,6 +512,8 @@ def main() -> int:
     ap.add_argument("--no-peak", action="store_true", help="skip the dense 8-bit peak measurement")
     ap.add_argument("--no-config5", action="store_true", help="skip the strong-scaling configuration")
     ap.add_argument("--accuracy", action="store_true", help="print the accuracy table and exit")
+    ap.add_argument("--no-outliers", action="store_true",
+                    help="profiling aid: inputs without the x50 key tokens (no key tile is negligible then)")
     ap.add_argument("--e2e-groups", type=int, default=0,
                     help="head groups a step of the end-to-end pipeline is issued as (0: the default)")
     ap.add_argument("--shape", default=None, metavar="H,N",
@@ -485,6 +522,9 @@ def main() -> int:
     if args.shape:
         global H, N
         H, N = (int(x) for x in args.shape.split(","))
+    if args.no_outliers:
+        global OUTLIER_FRAC
+        OUTLIER_FRAC = 0.0
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
@@ -565,12 +605,13 @@ def main() -> int:
     # The prologue lasts about half a millisecond: timed call by call from an idle GPU, the host's
     # launch latency before the first kernel would be counted as kernel time.  So it is timed as a
     # back-to-back batch (the GPU is still busy with call i when call i+1 is enqueued).
+    pro_iters = max(args.steps, 20)
     ev[0].record(stream)
-    for _ in range(args.steps):
+    for _ in range(pro_iters):
         pq = be.quant_qkv(q, k, v, reuse=pq)
     ev[1].record(stream)
     torch.cuda.synchronize(dev)
-    pro = ev[0].elapsed_time(ev[1]) / args.steps
+    pro = ev[0].elapsed_time(ev[1]) / pro_iters
     pk = peaks()
     achieved = flops(causal) / (att * 1e-3) / 1e12
     # The yardstick: this GPU's own dense 8-bit rate, measured in this run on rank 0 (the other

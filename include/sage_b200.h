@@ -24,6 +24,14 @@ extern "C" {
 
 enum { SAGE_F16 = 0, SAGE_BF16 = 1 };            /* element type of q, k, v and of the output  */
 enum { SAGE_QK_INT8 = 0, SAGE_QK_E4M3 = 1 };     /* code type of the quantised Q and K         */
+/* May be ORed into the qk_mode of the attention entry points (sage_attn_fwd*, sage_attention*; for
+ * the "default" mode of sage_attention* pass -SAGE_QK_NO_FAST_PATH instead of -1): the attention
+ * kernel then runs without its negligible-tile tests.  Those tests skip the exponentials of key
+ * tiles that lie at least 40 exponent units below the running row maxima (see
+ * sage_debug_skip_threshold); they cost 3 to 6 % on inputs where no tile can be skipped, so a
+ * host that knows its inputs have no dominant keys switches them off.  The Python package does so
+ * by itself from the skipped-tile counts of earlier calls. */
+#define SAGE_QK_NO_FAST_PATH 0x100
 
 enum {
   SAGE_OK = 0,
@@ -73,7 +81,7 @@ size_t sage_prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
  *   ctrl      sage_prologue_ctrl_bytes() of scratch; contents need not be initialised.  After the
  *             call its 32-bit word number 4*B*H is non-zero if a bounded wait inside the quantiser
  *             ran out (the outputs are then undefined); sage_attention reports the same event as
- *             bit 8 of its status word
+ *             the value 8 ORed into its status word
  *   N_pad     must equal sage_pad_len(N)
  * Alignment: q, k, v, q8, k8, v8t, sk, sv, svp and ctrl (and vmean of sage_prologue_ex) are read or
  * written with 16-byte vector accesses and must be 16-byte aligned; a misaligned one is refused
@@ -106,7 +114,7 @@ int sage_prologue(const void* q, const void* k, const void* v,
  *     order them, or give one of them its own scratch through sage_prologue.
  *   - `status` (optional, may be NULL): one int32 in the caller's device memory.  The quantiser's
  *     own failure flag lives inside the built-in array, which the caller cannot read, so a
- *     bounded wait that ran out is reported here instead: bit 8 (0x100) is ORed into the word and
+ *     bounded wait that ran out is reported here instead: the value 8 is ORed into the word and
  *     the outputs of that call are undefined.  The call never clears the word; zero it once and
  *     read it whenever the stream is known to have passed the call. */
 size_t sage_prologue_static_ctrl_capacity(void);
@@ -138,21 +146,33 @@ int sage_attn_fwd(const void* q8, const float* sq, const void* k8, const float* 
                   int causal, float sm_scale, int out_dtype, int qk_mode,
                   int32_t* status, void* stream);
 
-/* Enqueue, on `stream`, a copy of one status word (device memory: the `status` of sage_attn_fwd,
- * or the word at offset 10 of sage_workspace_layout) into `status_host`, which should be pinned
+/* Enqueue, on `stream`, a copy of `words` (1..4) 32-bit words starting at a status word (device
+ * memory: the `status` of sage_attn_fwd with words = 1, or the word at offset 10 of
+ * sage_workspace_layout, where word 3 after it counts the (warp, key tile) pairs the attention
+ * kernel's fast path skipped in that call: 16 warps per pair of query tiles, so the count divided
+ * by 8 * query tiles * key tiles * heads is the skipped share) into `status_host`, which should be pinned
  * host memory so that the copy does not block.  Nothing synchronises: once the stream has passed
  * this point the host word holds the call's status, non-zero after a bounded wait ran out.  This
  * is how a host learns of a device-side failure without waiting for every call; the reference
  * raises for such failures only in strict mode and otherwise falls back
  * (sageattention/sk1_backend/__init__.py:1022-1027,1114-1123).  Status bits: 1 TMA producer,
- * 2 MMA issuer, 4 softmax warp of the attention kernel; 0x100 tile load of the prologue. */
-int sage_status_mirror(const int32_t* status_dev, int32_t* status_host, void* stream);
+ * 2 MMA issuer, 4 softmax warp of the attention kernel; 8 tile load of the prologue. */
+int sage_status_mirror(const int32_t* status_dev, int32_t* status_host, int words, void* stream);
 
 /* Test hook (one process-wide atomic word): the attention kernel has two shapes, one or two
  * 128-query tiles per CTA, and picks the one it expects to finish sooner for the call's size.
  * n = 1 or 2 forces that shape for later launches from any thread, anything else restores the
  * automatic choice.  Both shapes give bit-identical results. */
 void sage_debug_tiles_per_cta(int n);
+
+/* Test hook (one process-wide atomic word): threshold of the attention kernel's negligible-tile
+ * fast path.  A key tile whose scores, for all 16 query rows a warp owns, lie at least
+ * `log2_units` below those rows' running maxima (in the base-2 exponent domain) is not
+ * exponentiated: its P entries are exact zeros either way (p * svp < 2^-40 * 448 rounds to the
+ * e4m3 zero) and the row sums lose less than 128 * 2^-log2_units of their largest term per tile.
+ * Default 40; 0 switches the path off (every tile is exponentiated, as the reference does:
+ * kernels/hip/sk1_t6i.hip:162-279); a negative value restores the default. */
+void sage_debug_skip_threshold(float log2_units);
 
 /* The shape the attention kernel takes, left to itself, for B x Hq heads of Nq queries on a device
  * with sm_count SMs: 1 or 2 query tiles per CTA (0 for bad arguments).  Host arithmetic only. */

@@ -48,37 +48,6 @@
 #include "sage_common.cuh"
 #include "sage_internal.h"
 
-// experiment knobs (defaults = shipped behaviour)
-#ifndef SAGE_SMEM_PLAIN
-#define SAGE_SMEM_PLAIN 0
-#endif
-#ifndef SAGE_LEAN_MMA
-#define SAGE_LEAN_MMA 0
-#endif
-#ifndef SAGE_POLY
-#define SAGE_POLY 0
-#endif
-#ifndef SAGE_PREFETCH
-#define SAGE_PREFETCH 0
-#endif
-// start the four softmax warps of a scheduler a quarter period apart (cycles per step; 0 = off)
-#ifndef SAGE_STAGGER
-#define SAGE_STAGGER 0
-#endif
-// timing-only ablations (wrong results): 1 no P stores, 2 no scale loads, 4 no P.V products, 8 no ex2
-#ifndef SAGE_ABL
-#define SAGE_ABL 0
-#endif
-
-#ifndef SAGE_SCALAR
-#define SAGE_SCALAR 0
-#endif
-#if SAGE_SCALAR
-#define __fmul2_rn(a, b) make_float2(__fmul_rn((a).x, (b).x), __fmul_rn((a).y, (b).y))
-#define __fadd2_rn(a, b) make_float2(__fadd_rn((a).x, (b).x), __fadd_rn((a).y, (b).y))
-#define __ffma2_rn(a, b, c) make_float2(__fmaf_rn((a).x, (b).x, (c).x), __fmaf_rn((a).y, (b).y, (c).y))
-#endif
-
 namespace sage {
 
 constexpr uint32_t TILE_BYTES = TILE * HD;          // 16 KiB: 128 rows x 128 one-byte codes
@@ -236,30 +205,6 @@ __device__ __forceinline__ void mma_ss(uint32_t d_tmem, uint64_t a_desc, uint64_
   }
 }
 
-// The same with the two 64-bit descriptors handed over as 32-bit halves (the upper halves are
-// compile-time constants, the lower ones differ by small constants between the k-steps).
-template <bool INT8>
-__device__ __forceinline__ void mma_ss_halves(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo,
-                                              uint32_t b_hi, uint32_t idesc, uint32_t accumulate) {
-  if (INT8) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], da, db, %5, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
-  } else {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tsetp.ne.b32 p, %6, 0;\n\t"
-        "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
-        "tcgen05.mma.cta_group::1.kind::f8f6f4 [%0], da, db, %5, p;\n\t}"
-        ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate) : "memory");
-  }
-}
-constexpr uint32_t DESC_HI_SW128 = (1024u >> 4) | (1u << 14) | (2u << 29);
-constexpr uint32_t DESC_HI_NOSW = (1024u >> 4) | (1u << 14);
-__device__ __forceinline__ uint32_t desc_lo_sw128(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | (1u << 16); }
-__device__ __forceinline__ uint32_t desc_lo_nosw(uint32_t saddr) { return ((saddr & 0x3FFFFu) >> 4) | ((128u >> 4) << 16); }
-
 // 16 lanes x 256 bits per repetition: thread t holds lanes t/4 (registers 4i, 4i+1) and t/4 + 8
 // (registers 4i+2, 4i+3), columns 8i + 2(t%4) and the next one; x8 = 64 columns, 32 registers.
 __device__ __forceinline__ void tmem_ld_16x256b_x8(uint32_t taddr, uint32_t* r) {
@@ -304,22 +249,6 @@ __device__ __forceinline__ float max3(float a, float b, float c) {
   return y;
 }
 
-// 2^t for two arguments t <= 0 on the FMA pipe: split t = n + f with n integral and |f| <= 1/2
-// (adding 1.5 * 2^23 leaves n in the low mantissa bits), a cubic for 2^f (relative error 7.5e-5)
-// and n added to the exponent field.  Arguments below -126 (masked scores are -inf) give 2^-126.
-__device__ __forceinline__ float2 ex2_poly2(float2 t) {
-  const float MAGIC = 12582912.f;
-  const float2 tc = make_float2(fmaxf(t.x, -126.f), fmaxf(t.y, -126.f));
-  const float2 r = __fadd2_rn(tc, make_float2(MAGIC, MAGIC));
-  const float2 nf = __fadd2_rn(r, make_float2(-MAGIC, -MAGIC));
-  const float2 f = __fadd2_rn(tc, make_float2(-nf.x, -nf.y));
-  float2 q = __ffma2_rn(f, make_float2(0.055171460f, 0.055171460f), make_float2(0.24261086f, 0.24261086f));
-  q = __ffma2_rn(q, f, make_float2(0.69326097f, 0.69326097f));
-  q = __ffma2_rn(q, f, make_float2(0.99992812f, 0.99992812f));
-  return make_float2(__int_as_float(__float_as_int(q.x) + (__float_as_int(r.x) << 23)),
-                     __int_as_float(__float_as_int(q.y) + (__float_as_int(r.y) << 23)));
-}
-
 // Shared-memory matrix descriptor of a K-major tile of 128-byte rows written with the 128-byte
 // swizzle (what TMA SWIZZLE_128B produces): 8-row groups 1024 bytes apart, descriptor version 1.
 __device__ __forceinline__ uint64_t kmajor_sw128_desc(uint32_t saddr) {
@@ -347,6 +276,8 @@ struct AttnKArgs {
   const float* vmean;             // optional (B*H, 128): added to every output row (smooth_v)
   long long o_sb, o_sh, o_sr;
   float sm_scale;
+  float skip_log2;    // FAST kernels: key tiles whose scores all lie this far (exponent domain) below the running maxima are not exponentiated
+  unsigned* skipped;  // FAST kernels, optional: receives the number of (warp, key tile) pairs that were skipped
   int32_t* status;
 };
 
@@ -364,7 +295,7 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 // The kernel.  NQ = 1: grid (ceil(Nq/128), B*Hq), block 384, two CTAs per SM; NQ = 2: grid
 // (ceil(Nq/256), B*Hq), block 640, one CTA per SM.
 // ------------------------------------------------------------------------------------------------
-template <bool INT8, bool CAUSAL, typename OutT, int NQ>
+template <bool INT8, bool CAUSAL, typename OutT, int NQ, bool FAST>
 __global__ void __launch_bounds__(Shape<NQ>::THREADS, Shape<NQ>::CTAS_PER_SM)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
@@ -468,54 +399,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const int g = warp - 1;
       const int gb = BAR_PER_TILE * g;
       const int n_tiles = tiles_of(g);
-#if SAGE_LEAN_MMA
-      if (lane == 0) {
-        constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
-        // Lower halves of the operand descriptors: a tile (stage, P buffer) further is +1024 in
-        // the address field, a k-step +2 (32 bytes of a swizzled row) or +16 (256 bytes: two
-        // 16-byte columns of the unswizzled P tile).
-        const uint32_t q_lo = desc_lo_sw128(base + OFF_Q + g * TILE_BYTES);
-        const uint32_t k_lo = desc_lo_sw128(base + OFF_K);
-        const uint32_t v_lo = desc_lo_sw128(base + OFF_V);
-        const uint32_t p_lo = desc_lo_nosw(base + OFF_P + g * L::P_BUFS * TILE_BYTES);
-        const uint32_t d_s = tmem + L::tmem_s(g), d_o = tmem + L::tmem_o(g);
-        const uint32_t b_kf = bar(BAR_KF), b_ke = bar(BAR_KE), b_vf = bar(BAR_VF), b_ve = bar(BAR_VE);
-        const uint32_t b_sf = bar(BAR_SF + gb), b_sfree = bar(BAR_SFREE + gb), b_pf = bar(BAR_PF + gb), b_pv = bar(BAR_PV + gb);
-        bool ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
-        for (int j = 0; ok && j <= n_tiles; ++j) {
-          if (j < n_tiles) {
-            const uint32_t s = (uint32_t)j & 1u;
-            ok = mbar_wait(b_kf + 8u * s, ((uint32_t)j >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
-            if (ok && j > 0) ok = mbar_wait(b_sfree, (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t kl = k_lo + 1024u * s;
-            mma_ss_halves<INT8>(d_s, q_lo + 0, DESC_HI_SW128, kl + 0, DESC_HI_SW128, IDESC_QK, 0u);
-            mma_ss_halves<INT8>(d_s, q_lo + 2, DESC_HI_SW128, kl + 2, DESC_HI_SW128, IDESC_QK, 1u);
-            mma_ss_halves<INT8>(d_s, q_lo + 4, DESC_HI_SW128, kl + 4, DESC_HI_SW128, IDESC_QK, 1u);
-            mma_ss_halves<INT8>(d_s, q_lo + 6, DESC_HI_SW128, kl + 6, DESC_HI_SW128, IDESC_QK, 1u);
-            tc_commit(b_ke + 8u * s);
-            tc_commit(b_sf);
-          }
-          if (j > 0) {
-            const uint32_t jj = (uint32_t)(j - 1);
-            const uint32_t s = (L::V_STAGES == 2) ? (jj & 1u) : 0u;
-            const uint32_t parv = (L::V_STAGES == 2) ? ((jj >> 1) & 1u) : (jj & 1u);
-            ok = mbar_wait(b_vf + 8u * s, parv, cta_abort, a.status, ST_TIMEOUT_MMA);
-            if (ok) ok = mbar_wait(b_pf, jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
-            if (!ok) break;
-            tc_fence_after();
-            const uint32_t pl = p_lo + 1024u * (jj & 1u), vl = v_lo + 1024u * s;
-            mma_ss_halves<false>(d_o, pl + 0, DESC_HI_NOSW, vl + 0, DESC_HI_SW128, IDESC_F8, jj > 0 ? 1u : 0u);
-            mma_ss_halves<false>(d_o, pl + 16, DESC_HI_NOSW, vl + 2, DESC_HI_SW128, IDESC_F8, 1u);
-            mma_ss_halves<false>(d_o, pl + 32, DESC_HI_NOSW, vl + 4, DESC_HI_SW128, IDESC_F8, 1u);
-            mma_ss_halves<false>(d_o, pl + 48, DESC_HI_NOSW, vl + 6, DESC_HI_SW128, IDESC_F8, 1u);
-            tc_commit(b_ve + 8u * s);
-            tc_commit(b_pv);
-          }
-        }
-      }
-#else
       if (lane == 0) {
         constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
         bool ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
@@ -540,7 +423,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             if (!ok) break;
             tc_fence_after();
 #pragma unroll
-            for (int k = 0; k < ((SAGE_ABL & 4) ? 0 : 4); ++k)
+            for (int k = 0; k < 4; ++k)
               mma_ss<false>(tmem + L::tmem_o(g),
                             kmajor_nosw_desc(base + OFF_P + (g * L::P_BUFS + (jj & (L::P_BUFS - 1))) * TILE_BYTES + 256 * k),
                             kmajor_sw128_desc(base + OFF_V + s * TILE_BYTES + 32 * k), IDESC_F8,
@@ -550,7 +433,6 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
         }
       }
-#endif
     } else if (warp >= 4) {
       // ------------------------------- softmax warps ------------------------------
       // A warp owns 16 TMEM lanes (query rows) and all 128 key columns, read with the 16x256b
@@ -585,70 +467,117 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
                           16u * (uint32_t)r0 + 4u * (uint32_t)c;
       const uint32_t sk_c = base + OFF_SK + 16u * (uint32_t)c;   // scales of keys 16m+4c..+3 at + 64m
 
+      // Negligible-tile fast path (kernels instantiated with FAST; the others carry none of it:
+      // any addition to the code between the row maxima and the exponentials, even two fused
+      // multiply-adds and a vote without a branch, costs 3 to 6 % on inputs where no tile can be
+      // skipped, so the host picks the instantiation).  A key tile whose every score lies
+      // a.skip_log2 (40) or more below the row's running maximum in the exponent domain, for all
+      // 16 rows of the warp, adds exact zeros to P (p * svp < 2^-40 * 448 rounds to the e4m3 zero)
+      // and less than 128 * 2^-40 of the row's largest term to its sum.  Such a tile is not
+      // exponentiated: the warp's P rows are zeros, the row sums and maxima stay as they are.  Two
+      // tests, both upper bounds of the tile's largest exponent formed with the same monotone
+      // operations as the exponents themselves:
+      //   after the conversion   t <= fma(row max of u, c_q, -c_q*m)
+      //   before the conversion  u <= fl(f32(max(row max of S, 0)) * max of the tile's sk)
+      // The second, cheaper one is tried when the warp's previous tile was skipped.
+      // Warp-uniform state: bit b (b < P_BUFS): this warp's rows of P tile b hold zeros; bit 8:
+      // the previous tile was skipped; bit 9: armed; bits 12-15: tests failed since the last skip.
+      uint32_t fast = 0;
+      constexpr uint32_t TRY_BOUND = 256u, ARMED = 512u, FAIL_ONE = 1u << 12, FAIL_MASK = 15u << 12;
+      int n_skipped = 0;                                    // tiles this warp skipped (reported once, at the end)
+      // What is left of a skipped tile: zeros for the warp's P rows (unless the tile already holds
+      // them), the wait for P.V(j-1) (see the comment at the other copy of this wait below) and
+      // the arrival at the P barrier.
+      auto finish_skipped = [&](int j) -> bool {
+        const uint32_t bit = 1u << (j & (L::P_BUFS - 1));
+        if (!(fast & bit)) {
+          const uint32_t pA = p0 + (uint32_t)(j & (L::P_BUFS - 1)) * TILE_BYTES, pB = pA + 8u * 128u;
+#pragma unroll
+          for (int m = 0; m < 8; ++m) { sts32u(pA + 128u * (uint32_t)m, 0u); sts32u(pB + 128u * (uint32_t)m, 0u); }
+        }
+        fast = (fast & ~FAIL_MASK) | bit | TRY_BOUND | ARMED;
+        ++n_skipped;
+        if (j > 0) {
+          const bool w = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
+          if (!__all_sync(0xffffffffu, w)) return false;
+          tc_fence_after();
+        }
+        fence_async_smem();
+        tc_fence_before();
+        __syncwarp();
+        mbar_arrive_lane0(bar(BAR_PF + gb), lane);
+        return true;
+      };
+
       for (int j = 0; j < n_tiles; ++j) {
         // S(j) complete implies the K stage, and with it this tile's scale rows, has landed
         ok = mbar_wait(bar(BAR_SF + gb), (uint32_t)j & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
         ok = __all_sync(0xffffffffu, ok);
         if (!ok) break;
-#if SAGE_STAGGER
-        if (j == 0) {
-          const long long hold = (long long)SAGE_STAGGER * (long long)(2 * g + sub);
-          const long long t0 = clock64();
-          while (clock64() - t0 < hold) { }
-        }
-#endif
         tc_fence_after();
         uint32_t acc[64];                                   // acc[8m + {0,1,4,5}]: row A keys +0..3; {2,3,6,7}: row B
-#if SAGE_ABL & 256
-#pragma unroll
-        for (int i = 0; i < 64; ++i) acc[i] = (uint32_t)(j + i);
-#else
         tmem_ld_16x256b_x16(t_s, acc);
         tmem_ld_wait();
-#endif
         tc_fence_before();
         __syncwarp();
         mbar_arrive_lane0(bar(BAR_SFREE + gb), lane);
-#if SAGE_ABL & 128
-        {
-          uint32_t x = 0;
-#pragma unroll
-          for (int i = 0; i < 64; ++i) x ^= acc[i];
-          if (x == 0x12345678u) lA += 1.f;                  // keeps the loads alive
-          if (j > 0) {
-            ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            tc_fence_after();
-          }
-          fence_async_smem();
-          tc_fence_before();
-          __syncwarp();
-          mbar_arrive_lane0(bar(BAR_PF + gb), lane);
-          continue;
-        }
-#endif
 
         const uint32_t skv = sk_c + (uint32_t)(j & 3) * VEC_BYTES;        // this tile's K scales
         const uint32_t svv = skv + (OFF_SV - OFF_SK);                      // and its staged V factors
-#if SAGE_SMEM_PLAIN
-        const uint8_t* sk_ptr = gbase + OFF_SK + 16 * c + (j & 3) * VEC_BYTES;
-        const uint8_t* sv_ptr = sk_ptr + (OFF_SV - OFF_SK);
-        uint8_t* pA_ptr = gbase + OFF_P + (g * L::P_BUFS + (j & (L::P_BUFS - 1))) * TILE_BYTES + lane_base * 128 + 16 * r0 + 4 * c;
-        uint8_t* pB_ptr = pA_ptr + 8 * 128;
-#endif
+        if (FAST && (fast & TRY_BOUND)) {
+          // largest K scale of the tile: lane l looks at keys 4l..4l+3
+          const float4 k4 = lds128(skv - 16u * (uint32_t)c + 16u * (uint32_t)lane);
+          float km = max3(fmaxf(k4.x, k4.y), k4.z, k4.w);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) km = fmaxf(km, __shfl_xor_sync(0xffffffffu, km, o));
+          float sA, sB;
+          if (INT8) {
+            int a0 = (int)acc[0], a1 = (int)acc[1], b0 = (int)acc[2], b1 = (int)acc[3];
+            a0 = __vimax3_s32(a0, (int)acc[4], (int)acc[5]);
+            b0 = __vimax3_s32(b0, (int)acc[6], (int)acc[7]);
+#pragma unroll
+            for (int m = 1; m < 8; ++m) {
+              a0 = __vimax3_s32(a0, (int)acc[8 * m + 0], (int)acc[8 * m + 1]);
+              a1 = __vimax3_s32(a1, (int)acc[8 * m + 4], (int)acc[8 * m + 5]);
+              b0 = __vimax3_s32(b0, (int)acc[8 * m + 2], (int)acc[8 * m + 3]);
+              b1 = __vimax3_s32(b1, (int)acc[8 * m + 6], (int)acc[8 * m + 7]);
+            }
+            int ia = max(max(a0, a1), 0), ib = max(max(b0, b1), 0);
+            ia = max(ia, __shfl_xor_sync(0xffffffffu, ia, 1)); ib = max(ib, __shfl_xor_sync(0xffffffffu, ib, 1));
+            ia = max(ia, __shfl_xor_sync(0xffffffffu, ia, 2)); ib = max(ib, __shfl_xor_sync(0xffffffffu, ib, 2));
+            sA = (float)ia; sB = (float)ib;
+          } else {
+            float a0 = __uint_as_float(acc[0]), a1 = __uint_as_float(acc[1]);
+            float b0 = __uint_as_float(acc[2]), b1 = __uint_as_float(acc[3]);
+            a0 = max3(a0, __uint_as_float(acc[4]), __uint_as_float(acc[5]));
+            b0 = max3(b0, __uint_as_float(acc[6]), __uint_as_float(acc[7]));
+#pragma unroll
+            for (int m = 1; m < 8; ++m) {
+              a0 = max3(a0, __uint_as_float(acc[8 * m + 0]), __uint_as_float(acc[8 * m + 1]));
+              a1 = max3(a1, __uint_as_float(acc[8 * m + 4]), __uint_as_float(acc[8 * m + 5]));
+              b0 = max3(b0, __uint_as_float(acc[8 * m + 2]), __uint_as_float(acc[8 * m + 3]));
+              b1 = max3(b1, __uint_as_float(acc[8 * m + 6]), __uint_as_float(acc[8 * m + 7]));
+            }
+            sA = max3(a0, a1, 0.f); sB = max3(b0, b1, 0.f);
+            sA = fmaxf(sA, __shfl_xor_sync(0xffffffffu, sA, 1)); sB = fmaxf(sB, __shfl_xor_sync(0xffffffffu, sB, 1));
+            sA = fmaxf(sA, __shfl_xor_sync(0xffffffffu, sA, 2)); sB = fmaxf(sB, __shfl_xor_sync(0xffffffffu, sB, 2));
+          }
+          // (a maximum that is still -inf makes the bound +inf: the comparison fails)
+          const float tA = __fmaf_rn(__fmul_rn(sA, km), cqA, -(cqA * mA));
+          const float tB = __fmaf_rn(__fmul_rn(sB, km), cqB, -(cqB * mB));
+          if (__all_sync(0xffffffffu, fmaxf(tA, tB) <= -a.skip_log2)) {
+            ok = finish_skipped(j);
+            if (!ok) break;
+            continue;
+          }
+          fast &= ~TRY_BOUND;
+        }
         float2 uA[16], uB[16];                              // u[2m], u[2m+1]: keys 16m+4c+{0,1}, +{2,3} (times sk)
 #pragma unroll
         for (int m = 0; m < 8; ++m) {
-#if SAGE_ABL & 2
-          const float4 kk = make_float4(cqA, cqB, cqA, cqB);
-#elif SAGE_SMEM_PLAIN
-          const float4 kk = *reinterpret_cast<const float4*>(sk_ptr + 64 * m);
-#else
           const float4 kk = lds128(skv + 64 * m);
-#endif
           float a0, a1, a2, a3, b0, b1, b2, b3;
-          if (INT8 && !(SAGE_ABL & 16)) {
+          if (INT8) {
             a0 = (float)(int)acc[8 * m + 0]; a1 = (float)(int)acc[8 * m + 1];
             b0 = (float)(int)acc[8 * m + 2]; b1 = (float)(int)acc[8 * m + 3];
             a2 = (float)(int)acc[8 * m + 4]; a3 = (float)(int)acc[8 * m + 5];
@@ -690,7 +619,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         }
         float xa0 = uA[0].x, xa1 = uA[0].y, xb0 = uB[0].x, xb1 = uB[0].y;
 #pragma unroll
-        for (int i = 1; i < ((SAGE_ABL & 32) ? 0 : 16); i += 2) {
+        for (int i = 1; i < 16; i += 2) {
           xa0 = max3(xa0, uA[i].x, uA[i].y);
           xb0 = max3(xb0, uB[i].x, uB[i].y);
           if (i + 1 < 16) {
@@ -707,85 +636,62 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const float mA_new = fmaxf(mA, mxA), mB_new = fmaxf(mB, mxB);
         const float mA_use = (mA_new == -INFINITY) ? 0.f : mA_new;
         const float mB_use = (mB_new == -INFINITY) ? 0.f : mB_new;
-        const float alphaA = ex2(cqA * (mA - mA_use)), alphaB = ex2(cqB * (mB - mB_use));
-
-        // The accumulator is rescaled after the exponentials, when the score registers are free;
-        // PV(j) is not issued before this warp arrives.
-        const bool rescale = (j > 0) && __any_sync(0xffffffffu, (mA_new > mA) || (mB_new > mB));
+        float alphaA, alphaB;
+        bool rescale;
+        if (FAST && ((fast & ARMED) || (j & 3) == 0)) {
+          // The first test.  A warp that has not skipped a tile lately makes it on every fourth
+          // tile only (the vote holds up the exponentials); one skipped tile arms it for every
+          // tile, sixteen tests failed in a row disarm it.
+          // One vote for both questions: bit 0 "a maximum moved", bit 1 "a row of mine has an
+          // exponent above the threshold".
+          const unsigned votes = __reduce_or_sync(0xffffffffu, ((mA_new > mA) || (mB_new > mB) ? 1u : 0u) |
+              (fmaxf(__fmaf_rn(mxA, cqA, -(cqA * mA_use)), __fmaf_rn(mxB, cqB, -(cqB * mB_use))) <= -a.skip_log2 ? 0u : 2u));
+          if (!(votes & 2u)) {
+            ok = finish_skipped(j);
+            if (!ok) break;
+            continue;
+          }
+          if (fast & ARMED) { fast += FAIL_ONE; if ((fast & FAIL_MASK) == FAIL_MASK) fast &= ~(ARMED | FAIL_MASK); }
+          alphaA = ex2(cqA * (mA - mA_use)); alphaB = ex2(cqB * (mB - mB_use));
+          rescale = (j > 0) && (votes & 1u);
+        } else {
+          alphaA = ex2(cqA * (mA - mA_use)); alphaB = ex2(cqB * (mB - mB_use));
+          // The accumulator is rescaled after the exponentials, when the score registers are
+          // free; PV(j) is not issued before this warp arrives.
+          rescale = (j > 0) && __any_sync(0xffffffffu, (mA_new > mA) || (mB_new > mB));
+        }
         mA = mA_new; mB = mB_new;
 
         const uint32_t pA = p0 + (uint32_t)(j & (L::P_BUFS - 1)) * TILE_BYTES, pB = pA + 8u * 128u;
         const float nmA = -(cqA * mA_use), nmB = -(cqB * mB_use);
         const float2 nmA2 = make_float2(nmA, nmA), nmB2 = make_float2(nmB, nmB);
         float2 psA = make_float2(0.f, 0.f), psB = make_float2(0.f, 0.f);
-        auto load_sv = [&](int m) -> float4 {
-#if SAGE_ABL & 2
-          return make_float4(cqB, cqA, cqB, cqA);
-#elif SAGE_SMEM_PLAIN
-          return *reinterpret_cast<const float4*>(sv_ptr + 64 * m);
-#else
-          return lds128(svv + 64 * m);
-#endif
-        };
-        // exponentials of a pair of scores; some pairs are evaluated on the FMA pipe
-        auto exp_pair = [&](float2 t, bool poly) -> float2 {
-#if SAGE_ABL & 8
-          return make_float2(t.x * t.x + 1.f, t.y * t.y + 1.f);
-#endif
-          if (!poly) return make_float2(ex2(t.x), ex2(t.y));
-          return ex2_poly2(t);
-        };
-#if SAGE_PREFETCH
-        float4 vv_next = load_sv(0);
-#endif
 #pragma unroll
         for (int m = 0; m < 8; ++m) {                       // 16 keys = one 16-byte chunk of a P row; 4 of them here
-#if SAGE_PREFETCH
-          const float4 vv = vv_next;
-          if (m + 1 < 8) vv_next = load_sv(m + 1);
-#else
-          const float4 vv = load_sv(m);
-#endif
+          const float4 vv = lds128(svv + 64 * m);
           const float2 v01 = make_float2(vv.x, vv.y), v23 = make_float2(vv.z, vv.w);
-          uint32_t wA, wB;
           {
             const float2 t0 = __ffma2_rn(uA[2 * m + 0], cqA2, nmA2);
             const float2 t1 = __ffma2_rn(uA[2 * m + 1], cqA2, nmA2);
-            const float2 p01 = exp_pair(t0, SAGE_POLY >= 1 && (m & 1) == 0 || SAGE_POLY >= 3);
-            const float2 p23 = exp_pair(t1, false);
+            const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
+            const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
             psA = __fadd2_rn(psA, __fadd2_rn(p01, p23));
             const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
-#if SAGE_ABL & 64
-            wA = __float_as_uint(f01.x) ^ __float_as_uint(f01.y) ^ __float_as_uint(f23.x) ^ __float_as_uint(f23.y);
-#else
-            wA = e4m3x4_pack(f01.x, f01.y, f23.x, f23.y);
-#endif
+            sts32u(pA + 128u * (uint32_t)m, e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
           }
           {
             const float2 t0 = __ffma2_rn(uB[2 * m + 0], cqB2, nmB2);
             const float2 t1 = __ffma2_rn(uB[2 * m + 1], cqB2, nmB2);
-            const float2 p01 = exp_pair(t0, false);
-            const float2 p23 = exp_pair(t1, SAGE_POLY >= 2 && (m & 1) == 1 || SAGE_POLY >= 3);
+            const float2 p01 = make_float2(ex2(t0.x), ex2(t0.y));
+            const float2 p23 = make_float2(ex2(t1.x), ex2(t1.y));
             psB = __fadd2_rn(psB, __fadd2_rn(p01, p23));
             const float2 f01 = __fmul2_rn(p01, v01), f23 = __fmul2_rn(p23, v23);
-#if SAGE_ABL & 64
-            wB = __float_as_uint(f01.x) ^ __float_as_uint(f01.y) ^ __float_as_uint(f23.x) ^ __float_as_uint(f23.y);
-#else
-            wB = e4m3x4_pack(f01.x, f01.y, f23.x, f23.y);
-#endif
+            sts32u(pB + 128u * (uint32_t)m, e4m3x4_pack(f01.x, f01.y, f23.x, f23.y));
           }
-#if SAGE_ABL & 1
-          if (wA == 0x12345678u && wB == 0x9abcdef0u) sts32u(pA, wA);   // keeps the values alive
-#elif SAGE_SMEM_PLAIN
-          *reinterpret_cast<uint32_t*>(pA_ptr + 128 * m) = wA;
-          *reinterpret_cast<uint32_t*>(pB_ptr + 128 * m) = wB;
-#else
-          sts32u(pA + 128u * (uint32_t)m, wA);
-          sts32u(pB + 128u * (uint32_t)m, wB);
-#endif
         }
         lA = lA * alphaA + (psA.x + psA.y);                 // this thread's quarter of the row sum
         lB = lB * alphaB + (psB.x + psB.y);
+        if (FAST) fast &= ~(1u << (j & (L::P_BUFS - 1)));
         // P.V(j-1) must be complete before the accumulator is rescaled.  The wait sits behind the
         // exponentials, where it does not stall: P(j) went to the tile that P.V(j-2) read, and that
         // product was waited for in the previous iteration.  It is made on every tile, rescaling
@@ -818,6 +724,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         __syncwarp();
         mbar_arrive_lane0(bar(BAR_PF + gb), lane);
       }
+
+      if (FAST && a.skipped != nullptr && lane == 0 && n_skipped > 0) atomicAdd(a.skipped, (unsigned)n_skipped);
 
       // ------------------------------- epilogue -----------------------------------
       if (ok) {
@@ -923,11 +831,16 @@ static bool make_map(CUtensorMap* m, const void* ptr, uint64_t inner, uint64_t r
 // choose_tiles_per_cta.  One relaxed atomic word; launches that race with a change take either value.
 static std::atomic<int> g_force_tiles_per_cta{0};
 void set_tiles_per_cta(int n) { g_force_tiles_per_cta.store((n == 1 || n == 2) ? n : 0, std::memory_order_relaxed); }
+// Test hook: the threshold of the negligible-tile fast path in log2 units (0 switches the path
+// off, a negative value restores the default).
+constexpr float SKIP_LOG2_DEFAULT = 40.f;
+static std::atomic<float> g_skip_log2{SKIP_LOG2_DEFAULT};
+void set_skip_log2(float t) { g_skip_log2.store(t < 0.f ? SKIP_LOG2_DEFAULT : t, std::memory_order_relaxed); }
 
-template <bool INT8, bool CAUSAL, typename OutT, int NQ>
+template <bool INT8, bool CAUSAL, typename OutT, int NQ, bool FAST>
 static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                                const AttnKArgs& ka, dim3 grid, cudaStream_t st) {
-  auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT, NQ>;
+  auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT, NQ, FAST>;
   using L = Shape<NQ>;
   // the opt-in to more than 48 KB of dynamic shared memory is per device and per instantiation;
   // it is made once (short calls are dominated by host-side work)
@@ -996,26 +909,30 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   const int forced = g_force_tiles_per_cta.load(std::memory_order_relaxed);
   if (forced != 0) two = (forced == 2);
   dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
+  // Which of the two sets of kernels: with the negligible-tile tests (the default) or without.
+  // The threshold hook at 0 and the caller's `no_fast_path` both select the plain set.
+  const float skip = g_skip_log2.load(std::memory_order_relaxed);
+  const bool fast = !p.no_fast_path && skip > 0.f;
+  ka.skip_log2 = skip;
+  ka.skipped = fast ? p.skipped : nullptr;
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
   cudaError_t e;
+#define SAGE_LAUNCH(I8, C, T)                                                                          \
+  e = two ? (fast ? launch_inst<I8, C, T, 2, true>(mq, mk, mv, ka, grid, st)                           \
+                  : launch_inst<I8, C, T, 2, false>(mq, mk, mv, ka, grid, st))                         \
+          : (fast ? launch_inst<I8, C, T, 1, true>(mq, mk, mv, ka, grid, st)                           \
+                  : launch_inst<I8, C, T, 1, false>(mq, mk, mv, ka, grid, st))
   switch (key) {
-    case 7: e = two ? launch_inst<true, true, __half, 2>(mq, mk, mv, ka, grid, st)
-                    : launch_inst<true, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
-    case 6: e = two ? launch_inst<true, true, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
-                    : launch_inst<true, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
-    case 5: e = two ? launch_inst<true, false, __half, 2>(mq, mk, mv, ka, grid, st)
-                    : launch_inst<true, false, __half, 1>(mq, mk, mv, ka, grid, st); break;
-    case 4: e = two ? launch_inst<true, false, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
-                    : launch_inst<true, false, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
-    case 3: e = two ? launch_inst<false, true, __half, 2>(mq, mk, mv, ka, grid, st)
-                    : launch_inst<false, true, __half, 1>(mq, mk, mv, ka, grid, st); break;
-    case 2: e = two ? launch_inst<false, true, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
-                    : launch_inst<false, true, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
-    case 1: e = two ? launch_inst<false, false, __half, 2>(mq, mk, mv, ka, grid, st)
-                    : launch_inst<false, false, __half, 1>(mq, mk, mv, ka, grid, st); break;
-    default: e = two ? launch_inst<false, false, __nv_bfloat16, 2>(mq, mk, mv, ka, grid, st)
-                     : launch_inst<false, false, __nv_bfloat16, 1>(mq, mk, mv, ka, grid, st); break;
+    case 7: SAGE_LAUNCH(true, true, __half); break;
+    case 6: SAGE_LAUNCH(true, true, __nv_bfloat16); break;
+    case 5: SAGE_LAUNCH(true, false, __half); break;
+    case 4: SAGE_LAUNCH(true, false, __nv_bfloat16); break;
+    case 3: SAGE_LAUNCH(false, true, __half); break;
+    case 2: SAGE_LAUNCH(false, true, __nv_bfloat16); break;
+    case 1: SAGE_LAUNCH(false, false, __half); break;
+    default: SAGE_LAUNCH(false, false, __nv_bfloat16); break;
   }
+#undef SAGE_LAUNCH
   if (e != cudaSuccess && why) *why = "attention kernel launch failed";
   return e;
 }

@@ -154,10 +154,12 @@ int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
               const void* v8t, const float* svp, const float* s_fold, void* out, float* lse, const float* qm,
               const float* vmean, const Dims& d, int64_t Nk_pad, const int64_t o_strides[3],
               int causal, float sm_scale, int out_dtype, int qk_mode, int32_t* status, void* stream,
-              const char* who) {
+              const char* who, unsigned* skipped = nullptr) {
   g_err[0] = 0;
   int rc = check_dims(d);
   if (rc) return rc;
+  const int no_fast_path = (qk_mode & SAGE_QK_NO_FAST_PATH) ? 1 : 0;
+  qk_mode &= ~SAGE_QK_NO_FAST_PATH;
   if (!q8 || !sq || !k8 || !sk || !v8t || !svp || !s_fold || !out || !status)
     return fail(SAGE_E_ARG, "%s: null pointer argument", who);
   if (Nk_pad != sage_pad_len(d.Nk)) return fail(SAGE_E_ARG, "%s: padded key length must be %lld", who, (long long)sage_pad_len(d.Nk));
@@ -179,6 +181,7 @@ int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
   for (int i = 0; i < 3; ++i) p.o_strides[i] = o_strides[i];
   p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.out_dtype = out_dtype; p.qk_mode = qk_mode;
   p.status = status;
+  p.no_fast_path = no_fast_path; p.skipped = skipped;
   const char* why = nullptr;
   cudaError_t e = sage::launch_attention(p, reinterpret_cast<cudaStream_t>(stream), &why);
   if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s (%s)", who, why ? why : "", cudaGetErrorString(e));
@@ -199,7 +202,9 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
   const Layout L = carve(d);
   if (workspace_bytes < L.total)
     return fail(SAGE_E_WORKSPACE, "%s: workspace has %zu bytes, needs %zu", who, workspace_bytes, L.total);
+  const int flags = (qk_mode >= 0) ? (qk_mode & SAGE_QK_NO_FAST_PATH) : (((-qk_mode) & SAGE_QK_NO_FAST_PATH));
   if (qk_mode < 0) qk_mode = (dtype == SAGE_BF16) ? SAGE_QK_E4M3 : SAGE_QK_INT8;
+  else qk_mode &= ~SAGE_QK_NO_FAST_PATH;
   char* w = reinterpret_cast<char*>(workspace);
   const int64_t Nk_pad = sage_pad_len(d.Nk);
   int32_t* status = reinterpret_cast<int32_t*>(w + L.status);     // zeroed by the prologue's memset
@@ -214,7 +219,8 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
   return attn_impl(w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
                    reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.svp),
                    reinterpret_cast<float*>(w + L.s_fold), out, lse, qm, vmean, d, Nk_pad, o_strides,
-                   causal, sm_scale, dtype, qk_mode, status, stream, who);
+                   causal, sm_scale, dtype, qk_mode | flags, status, stream, who,
+                   reinterpret_cast<unsigned*>(status) + 3);
 }
 
 }  // namespace
@@ -301,18 +307,21 @@ int sage_attn_fwd_ex(const void* q8, const float* sq, const void* k8, const floa
                    causal, sm_scale, out_dtype, qk_mode, status, stream, "sage_attn_fwd_ex");
 }
 
-int sage_status_mirror(const int32_t* status_dev, int32_t* status_host, void* stream) {
+int sage_status_mirror(const int32_t* status_dev, int32_t* status_host, int words, void* stream) {
   g_err[0] = 0;
   if (!status_dev || !status_host) return fail(SAGE_E_ARG, "sage_status_mirror: null pointer argument");
+  if (words < 1 || words > 4) return fail(SAGE_E_ARG, "sage_status_mirror: words must be 1..4");
   if ((reinterpret_cast<uintptr_t>(status_dev) | reinterpret_cast<uintptr_t>(status_host)) & 3u)
     return fail(SAGE_E_ARG, "sage_status_mirror: pointers must be 4-byte aligned");
-  cudaError_t e = cudaMemcpyAsync(status_host, status_dev, sizeof(int32_t), cudaMemcpyDeviceToHost,
+  cudaError_t e = cudaMemcpyAsync(status_host, status_dev, sizeof(int32_t) * (size_t)words, cudaMemcpyDeviceToHost,
                                   reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(SAGE_E_CUDA, "sage_status_mirror: %s", cudaGetErrorString(e));
   return SAGE_OK;
 }
 
 void sage_debug_tiles_per_cta(int n) { sage::set_tiles_per_cta(n); }
+
+void sage_debug_skip_threshold(float log2_units) { sage::set_skip_log2(log2_units); }
 
 int sage_attention_tiles_per_cta(int64_t B, int64_t Hq, int64_t Nq, int causal, int sm_count) {
   if (B < 1 || Hq < 1 || Nq < 1 || sm_count < 1) return 0;

@@ -23,7 +23,9 @@ struct CtrlHeader {
   // (non-zero when a wait inside the quantiser ran out), one pad word and the quantiser's 64-bit
   // work counter; the fp64 partial sums (shared by the two mean launches, which run one after the
   // other) follow at `partial_off`.
-  static __host__ __device__ inline size_t words(int64_t bh) { return (size_t)4 * (size_t)bh + 4; }
+  // (four more words follow the work counter: the attention kernel's count of skipped
+  // (warp, key tile) pairs, then three spare words; all of them are cleared by the same memset)
+  static __host__ __device__ inline size_t words(int64_t bh) { return (size_t)4 * (size_t)bh + 8; }
   static __host__ __device__ inline size_t status_word(int64_t bh) { return (size_t)4 * (size_t)bh; }
   static __host__ __device__ inline size_t partial_off(int64_t bh) {
     return (words(bh) * 4 + 255) / 256 * 256;

@@ -39,6 +39,8 @@ struct AttnParams {
   int out_dtype;  // 0 fp16, 1 bf16
   int qk_mode;    // 0 int8, 1 e4m3
   int32_t* status;
+  int no_fast_path;                                    // 1: the kernels without the negligible-tile tests
+  unsigned* skipped;                                   // optional: (warp, key tile) pairs the fast path skipped
 };
 
 cudaError_t launch_prologue(const PrologueParams& p, cudaStream_t st);
@@ -49,6 +51,8 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
 
 // Test hook: force the attention kernel's shape (1 or 2 query tiles per CTA; 0 = automatic).
 void set_tiles_per_cta(int n);
+// Test hook: threshold (log2 units) of the attention kernel's negligible-tile fast path; 0 = off, < 0 = default.
+void set_skip_log2(float t);
 int choose_tiles_per_cta(int64_t q_tiles, int64_t bhq, bool causal, int sms);
 
 }  // namespace sage

@@ -16,6 +16,7 @@ LIB_PATH = os.path.join(_HERE, "libsage_b200.so")
 
 SAGE_F16, SAGE_BF16 = 0, 1
 SAGE_QK_INT8, SAGE_QK_E4M3 = 0, 1
+SAGE_QK_NO_FAST_PATH = 0x100
 SAGE_E_ARG, SAGE_E_UNSUPPORTED, SAGE_E_CUDA, SAGE_E_WORKSPACE = -1, -2, -3, -4
 
 _I64 = ctypes.c_int64
@@ -49,8 +50,9 @@ SIGNATURES = {
     "sage_attention_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, ctypes.c_size_t, _I64, _I64, _I64, _I64, _I64, _I64,
                                          _S3, _S3, _S3, _S3, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_int, ctypes.c_int, ctypes.c_float, _P]),
-    "sage_status_mirror": (ctypes.c_int, [_P, _P, _P]),
+    "sage_status_mirror": (ctypes.c_int, [_P, _P, ctypes.c_int, _P]),
     "sage_debug_tiles_per_cta": (None, [ctypes.c_int]),
+    "sage_debug_skip_threshold": (None, [ctypes.c_float]),
     "sage_attention_tiles_per_cta": (ctypes.c_int, [_I64, _I64, _I64, ctypes.c_int, ctypes.c_int]),
     "sage_workspace_bytes": (ctypes.c_size_t, [_I64, _I64, _I64]),
     "sage_workspace_layout": (ctypes.c_int, [_I64, _I64, _I64, ctypes.POINTER(ctypes.c_size_t)]),

@@ -197,9 +197,10 @@ def quant_qkv(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, smooth_k: bool 
 
 
 def attn_launch(pq: Dict[str, torch.Tensor], out: torch.Tensor, is_causal: bool, sm_scale: float,
-                status: Optional[torch.Tensor] = None) -> torch.Tensor:
+                status: Optional[torch.Tensor] = None, plain: bool = False) -> torch.Tensor:
     """Launch the attention kernel on a prologue result; `out` is a logical (B,H,N,D) view that
-    is written in place.  Returns the int32 status tensor (zero unless a bounded wait gave up)."""
+    is written in place.  Returns the int32 status tensor (zero unless a bounded wait gave up).
+    `plain` selects the kernels without the negligible-tile tests."""
     lib = _native.load()
     dev = out.device
     b, h, n, n_pad = pq["B"], pq["H"], pq["n"], pq["n_pad"]
@@ -210,7 +211,8 @@ def attn_launch(pq: Dict[str, torch.Tensor], out: torch.Tensor, is_causal: bool,
             _ptr(pq["q8"]), _ptr(pq["sq"]), _ptr(pq["k8"]), _ptr(pq["sk"]), _ptr(pq["v8t"]),
             _ptr(pq["svp"]), _ptr(pq["S"]), _ptr(out), b, h, n, n_pad, _bhr(out),
             1 if is_causal else 0, float(sm_scale), _dtype_code(out.dtype),
-            _native.SAGE_QK_INT8 if pq["int8"] else _native.SAGE_QK_E4M3, _ptr(status), _stream(dev))
+            (_native.SAGE_QK_INT8 if pq["int8"] else _native.SAGE_QK_E4M3) |
+            (_native.SAGE_QK_NO_FAST_PATH if plain else 0), _ptr(status), _stream(dev))
     _native.check(rc, "sage_attn_fwd")
     return status
 
@@ -226,7 +228,7 @@ def attn_launch(pq: Dict[str, torch.Tensor], out: torch.Tensor, is_causal: bool,
 # SAGEATTN_B200_STRICT=1 synchronises after every call and checks at once;
 # SAGEATTN_B200_WATCH=0 switches the copy off.
 STATUS_BITS = ((1, "the TMA producer of the attention kernel"), (2, "the MMA issuer of the attention kernel"),
-               (4, "a softmax warp of the attention kernel"), (0x100, "a tile load of the quantisation prologue"))
+               (4, "a softmax warp of the attention kernel"), (8, "a tile load of the quantisation prologue"))
 
 
 def describe_status(code: int) -> str:
@@ -242,14 +244,66 @@ def _env_flag(name: str, default: bool) -> bool:
     return v.strip().lower() not in ("0", "false", "off", "no")
 
 
+# ---- which attention kernels a call takes ---------------------------------------------------------
+# The attention kernel exists with and without its negligible-tile tests (include/sage_b200.h,
+# SAGE_QK_NO_FAST_PATH).  With them, key tiles far below the running row maxima are not
+# exponentiated, which on inputs with a few dominant keys removes most of the softmax work; on
+# inputs without such keys the tests only cost (3 to 6 %).  The kernels count what they skip, so
+# the choice is made from evidence: a call signature (shape, mask, dtype) starts with the tests
+# on; one such call is a probe whose count comes back to the host with the status mirror (no
+# synchronisation: the result is picked up by a later call once its event has completed); a probe
+# that skipped less than PROBE_MIN_SHARE of the (warp, key tile) pairs sends the next PLAIN_CALLS
+# calls of that signature to the kernels without the tests, after which the next call probes
+# again.  Both sets of kernels give identical bits whenever no tile is skipped.
+PROBE_MIN_SHARE = 0.02
+PLAIN_CALLS = 255
+PROBE_AGAIN_AFTER = 256       # calls with the tests on between two probes
+
+
+class _Adaptive:
+    """Per (device, stream): the decision per call signature and the one outstanding probe."""
+
+    __slots__ = ("plain_left", "since_probe", "probe")
+
+    def __init__(self):
+        self.plain_left: Dict[Tuple, int] = {}     # signature -> calls left without the tests
+        self.since_probe: Dict[Tuple, int] = {}    # signature -> calls with the tests on since its last probe
+        self.probe = None                          # (signature, pairs, event, pinned tensor, ctypes words) or None
+
+    def decide(self, key: Tuple) -> Tuple[bool, bool]:
+        """(use the plain kernels, make this call a probe)."""
+        left = self.plain_left.get(key, 0)
+        if left > 0:
+            self.plain_left[key] = left - 1
+            return True, False
+        n = self.since_probe.get(key)
+        want_probe = n is None or n >= PROBE_AGAIN_AFTER
+        if want_probe and self.probe is None:
+            self.since_probe[key] = 0
+            return False, True
+        if n is not None:                       # (a signature that never got its probe keeps asking)
+            self.since_probe[key] = n + 1
+        return False, False
+
+    def take_result(self, key: Tuple, skipped: int, pairs: int) -> float:
+        share = float(skipped) / float(max(pairs, 1))
+        if share < PROBE_MIN_SHARE:
+            self.plain_left[key] = PLAIN_CALLS
+            self.since_probe.pop(key, None)
+        return share
+
+
 class _StreamState:
     """What the path keeps per (device, stream): one grow-only workspace (intermediates of a call
     live only until its attention kernel has run, and calls on one stream are ordered) and the
     pinned host word that mirrors the status word of the most recent call."""
 
-    __slots__ = ("ws", "host", "host_word", "status_off", "shape")
+    __slots__ = ("ws", "host", "host_word", "status_off", "shape", "adaptive", "probe_host", "last_share")
 
     def __init__(self, host_word=None):
+        self.adaptive = _Adaptive()
+        self.probe_host = None              # pinned (4,) int32 the probe's words land in
+        self.last_share = None              # share of skipped pairs in the most recent finished probe
         self.ws = None
         self.host = None                    # pinned tensor that owns the memory behind host_word
         self.host_word = host_word          # ctypes.c_int32 view of it (tests pass a plain c_int32)
@@ -268,6 +322,7 @@ class _StreamState:
 
 _STRICT = _env_flag("SAGEATTN_B200_STRICT", False)
 _WATCH = _env_flag("SAGEATTN_B200_WATCH", True) or _STRICT
+_ADAPTIVE = _env_flag("SAGEATTN_B200_ADAPTIVE", True)      # 0: every call keeps the negligible-tile tests
 
 _ws_lock = threading.Lock()
 _states: "OrderedDict[Tuple[int, int], _StreamState]" = OrderedDict()
@@ -316,6 +371,15 @@ def _host_word(st: _StreamState):
 def clear_workspaces():
     with _ws_lock:
         _states.clear()
+
+
+def reset_adaptive():
+    """Forget what earlier calls taught about which call signatures skip key tiles (every
+    signature probes again).  For callers whose data changes character under an unchanged shape."""
+    with _ws_lock:
+        for st in _states.values():
+            st.adaptive = _Adaptive()
+            st.last_share = None
 
 
 def check(device=None):
@@ -426,19 +490,47 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     st.status_off, st.shape = status_off, (b, h, hkv, n, nk)
     lse = torch.empty((b, h, n), dtype=torch.float32, device=dev) if return_lse else None
     ws_ptr = ws.data_ptr()
+    # with or without the negligible-tile tests (see _Adaptive)
+    # (while the stream is being captured into a CUDA graph nothing here may allocate, record or
+    # query an event: the call then takes the kernels the signature is on, without probing)
+    capturing = torch.cuda.is_current_stream_capturing()
+    ad = st.adaptive
+    if not capturing and ad.probe is not None and ad.probe[2].query():
+        pkey, pairs, _ev, words = ad.probe
+        ad.probe = None
+        st.last_share = ad.take_result(pkey, int(words[3]) & 0xFFFFFFFF, pairs)
+    key = (b, h, hkv, n, nk, d, bool(is_causal), dt, qk_mode)
+    if capturing:
+        plain, probe = ad.plain_left.get(key, 0) > 0, False
+    else:
+        plain, probe = ad.decide(key) if _ADAPTIVE else (False, False)
+    if plain:
+        qk_mode = -_native.SAGE_QK_NO_FAST_PATH if qk_mode < 0 else (qk_mode | _native.SAGE_QK_NO_FAST_PATH)
     args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), 0 if lse is None else lse.data_ptr(),
             ws_ptr, ws.numel(), b, h, hkv, n, nk, d, q3, k3, v3, o3, dt, qk_mode,
             1 if is_causal else 0, 1 if smooth_k else 0, 1 if smooth_v else 0, scale, stream_id)
-    watch = _WATCH
-    if torch.cuda.current_device() == dev.index:
+    watch = _WATCH and not (capturing and st.host_word is None)
+    same_dev = torch.cuda.current_device() == dev.index
+    if not same_dev:
+        prev_dev = torch.cuda.current_device()
+        torch.cuda.set_device(dev)
+    try:
         rc = lib.sage_attention_ex(*args)
         if watch and not rc:
-            rc = lib.sage_status_mirror(ws_ptr + status_off, ctypes.addressof(_host_word(st)), stream_id)
-    else:
-        with torch.cuda.device(dev):
-            rc = lib.sage_attention_ex(*args)
-            if watch and not rc:
-                rc = lib.sage_status_mirror(ws_ptr + status_off, ctypes.addressof(_host_word(st)), stream_id)
+            rc = lib.sage_status_mirror(ws_ptr + status_off, ctypes.addressof(_host_word(st)), 1, stream_id)
+        if probe and not rc:
+            if st.probe_host is None:
+                st.probe_host = torch.zeros((4,), dtype=torch.int32).pin_memory()
+            words = (ctypes.c_int32 * 4).from_address(st.probe_host.data_ptr())
+            rc = lib.sage_status_mirror(ws_ptr + status_off, ctypes.addressof(words), 4, stream_id)
+            ev = torch.cuda.Event()
+            ev.record(torch.cuda.current_stream(dev))
+            q_tiles, k_tiles = (n + TILE - 1) // TILE, (nk + TILE - 1) // TILE
+            pairs = 8 * b * h * q_tiles * k_tiles // (2 if is_causal else 1)
+            ad.probe = (key, pairs, ev, words)
+    finally:
+        if not same_dev:
+            torch.cuda.set_device(prev_dev)
     if rc:
         _native.check(rc, "sage_attention_ex")
     if _STRICT:
@@ -499,6 +591,10 @@ def status() -> dict:
                 strict=_STRICT, watch=_WATCH)
     with _ws_lock:
         info["device_status"] = {key: st.pending() for key, st in _states.items() if st.pending()}
+        info["fast_path"] = {key: dict(last_probe_share=st.last_share,
+                                       signatures_on_plain_kernels=sum(1 for v in st.adaptive.plain_left.values() if v > 0))
+                             for key, st in _states.items()}
+    info["adaptive"] = _ADAPTIVE
     try:
         info["version"] = _native.load().sage_version()
     except _native.SageNativeError as exc:

@@ -172,3 +172,58 @@ def test_video_length_properties():
     ref = torch.matmul(torch.softmax(s, -1), v[0, 0].float())
     e_gpu, e_ora = R.rel_rms(out[0, 0, rows], ref), R.rel_rms(o64[0, 0, rows], ref)
     assert e_gpu <= 1.1 * e_ora + 1e-3
+
+
+def test_device_status_reaches_the_caller_as_an_exception():
+    """The host learns of a device-side failure from a 4-byte copy of the status word that follows
+    every call (no synchronisation on the hot path).  No wait is made to run out here: the copy is
+    fed a word that already holds a code, and the next call, `check()` and `status()` must report
+    it; a healthy call leaves nothing behind."""
+    import ctypes
+    from sageattention import _native
+    lib = _native.load()
+    q, k, v = R.make_inputs(1, 2, 300, seed=6, device="cuda")
+    out = sageattention.sageattn(q, k, v)
+    be.check()                                                       # waits, finds nothing
+    assert be.status()["device_status"] == {}
+    dev, stream = q.device, torch.cuda.current_stream().cuda_stream
+    st = be._state(dev, stream, create=False)
+    assert st is not None and st.pending() == 0
+    word = torch.tensor([2 | 8], dtype=torch.int32, device="cuda")   # "MMA issuer" and "prologue"
+    assert lib.sage_status_mirror(word.data_ptr(), ctypes.addressof(be._host_word(st)), 1, stream) == 0
+    torch.cuda.synchronize()
+    assert list(be.status()["device_status"].values()) == [10]
+    with pytest.raises(RuntimeError, match="MMA issuer"):
+        sageattention.sageattn(q, k, v)                              # reported at the next call, before it launches
+    again = sageattention.sageattn(q, k, v)                          # reported once; the path works on
+    be.check()
+    assert torch.equal(out, again)
+    # strict mode: every call synchronises and checks
+    assert lib.sage_status_mirror(word.data_ptr(), ctypes.addressof(be._host_word(st)), 1, stream) == 0
+    torch.cuda.synchronize()
+    with pytest.raises(RuntimeError, match="prologue"):
+        be.check()
+    be._STRICT = True
+    try:
+        assert torch.equal(sageattention.sageattn(q, k, v), out)
+    finally:
+        be._STRICT = False
+
+
+@pytest.mark.parametrize("scale", [0.0, -0.5, float("inf"), float("nan")])
+def test_sm_scale_must_be_finite_and_positive(scale):
+    q, k, v = R.make_inputs(1, 1, 64, seed=1, device="cuda")
+    with pytest.raises(ValueError, match="sm_scale"):
+        sageattention.sageattn(q, k, v, sm_scale=scale)
+
+
+def test_last_status_does_not_invent_a_workspace():
+    q, k, v = R.make_inputs(1, 2, 200, seed=2, device="cuda")
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        with pytest.raises(RuntimeError, match="no call has run"):
+            be.last_status(q, 1, 2, 200)
+    sageattention.sageattn(q, k, v)
+    assert be.last_status(q, 1, 2, 200) == 0
+    with pytest.raises(RuntimeError, match="had shape"):
+        be.last_status(q, 1, 2, 201)

@@ -164,11 +164,11 @@ def test_device_status_codes_become_exceptions():
     with pytest.raises(RuntimeError, match="MMA issuer"):
         st.raise_if_failed("test")
     assert word.value == 0 and st.pending() == 0
-    word.value = 0x100 | 4
+    word.value = 8 | 4
     with pytest.raises(RuntimeError) as exc:
         st.raise_if_failed("the next call on the stream")
     msg = str(exc.value)
-    assert "0x104" in msg and "softmax warp" in msg and "prologue" in msg and "undefined" in msg
+    assert "0xc" in msg and "softmax warp" in msg and "prologue" in msg and "undefined" in msg
     assert "unknown role" in be.describe_status(0x40)
     assert be.status()["watch"] in (True, False) and "device_status" in be.status()
 
@@ -184,3 +184,26 @@ def test_strict_and_watch_switches_are_read_from_the_environment():
     assert run({"SAGEATTN_B200_STRICT": "1", "SAGEATTN_B200_WATCH": "0"}) == ["1", "1"]     # strict needs the copy
     assert run({"SAGEATTN_B200_STRICT": "0", "SAGEATTN_B200_WATCH": "0"}) == ["0", "0"]
 
+
+
+def test_choice_between_the_two_sets_of_attention_kernels():
+    """Host logic only: a signature starts with the negligible-tile tests on and one probing call;
+    a probe that skipped next to nothing buys PLAIN_CALLS calls on the kernels without the tests,
+    then the signature probes again; a probe that skipped a lot keeps the tests on; only one probe
+    is outstanding at a time, and a signature that could not probe keeps asking."""
+    a = be._Adaptive()
+    k1, k2 = ("sig", 1), ("sig", 2)
+    assert a.decide(k1) == (False, True)
+    a.probe = ("placeholder",)
+    assert a.decide(k1) == (False, False) and a.decide(k2) == (False, False)
+    a.probe = None
+    assert a.decide(k2) == (False, True)                         # k2 never got its probe: it asks again
+    assert a.take_result(k1, 3, 1000) < be.PROBE_MIN_SHARE
+    for _ in range(be.PLAIN_CALLS):
+        assert a.decide(k1) == (True, False)
+    assert a.decide(k1) == (False, True)                         # back to the tests, probing
+    assert a.take_result(k1, 600, 1000) == 0.6
+    assert a.decide(k1) == (False, False)
+    for _ in range(be.PROBE_AGAIN_AFTER - 1):
+        a.decide(k1)
+    assert a.decide(k1) == (False, True)
