@@ -494,7 +494,7 @@ def run_reference(args) -> int:
 def workload_config(causal: bool, gpus: int) -> dict:
     return dict(workload="video-length attention B=%d(per GPU) H=%d N=%d D=%d fp16 %s smooth_k, %s"
                 % (B, H, N, D, "causal" if causal else "non-causal",
-                   "0.1% K tokens x50" if OUTLIER_FRAC else "no dominant keys (profiling aid)"),
+                   ("%.2g%% K tokens x50" % (100 * OUTLIER_FRAC)) if OUTLIER_FRAC else "no dominant keys (profiling aid)"),
                 global_batch=B * gpus, heads=H, seq_len=N, head_dim=D, causal=causal, seed=SEED,
                 sharding="batch x head units across GPUs, no collective" if gpus > 1 else "single GPU",
                 l2="inputs (3 x 584 MB) exceed the 126 MB L2; no explicit flush")
@@ -514,6 +514,9 @@ def main() -> int:
     ap.add_argument("--accuracy", action="store_true", help="print the accuracy table and exit")
     ap.add_argument("--no-outliers", action="store_true",
                     help="profiling aid: inputs without the x50 key tokens (no key tile is negligible then)")
+    ap.add_argument("--outlier-frac", type=float, default=None,
+                    help="profiling aid: another share of x50 key tokens (a small --shape with as many such "
+                         "tokens as the full-size workload skips a comparable share of its key tiles)")
     ap.add_argument("--e2e-groups", type=int, default=0,
                     help="head groups a step of the end-to-end pipeline is issued as (0: the default)")
     ap.add_argument("--shape", default=None, metavar="H,N",
@@ -522,9 +525,11 @@ def main() -> int:
     if args.shape:
         global H, N
         H, N = (int(x) for x in args.shape.split(","))
+    global OUTLIER_FRAC
     if args.no_outliers:
-        global OUTLIER_FRAC
         OUTLIER_FRAC = 0.0
+    elif args.outlier_frac is not None:
+        OUTLIER_FRAC = float(args.outlier_frac)
     args.warmup = max(args.warmup, 3) if args.impl == "ours" else args.warmup
     if args.impl == "reference":
         return run_reference(args)
