@@ -38,6 +38,12 @@
 // c_q and sk are applied one after the other instead of as one pre-multiplied factor, a
 // difference of one rounding in a quantity the reference does not pin bit-wise)
 //
+// Every kernel is instantiated twice (template parameter FAST).  The FAST kernels test every key
+// tile against the running row maxima and do not exponentiate a tile whose scores all lie 40
+// exponent units or more below them (its P entries are exact zeros either way); they count what
+// they skip.  The others carry none of that code, and the host chooses between the two sets
+// (see the comment at the softmax warps' loop and launch_attention).
+//
 // Every wait on an mbarrier is bounded: after about two seconds, or as soon as another CTA has
 // reported a failure, the waiter records a code in the status word, the CTA drains and frees its
 // TMEM, and CTAs that start later return at once.

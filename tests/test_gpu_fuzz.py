@@ -67,3 +67,54 @@ def test_random_call(seed):
     assert R.rel_rms(o, ref) <= 1.05 * R.rel_rms(want_o, ref) + 2e-3, c
     if lse is not None:
         assert (lse.cpu() - want_l).abs().max().item() < 3e-3, c
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_random_call_with_dominant_keys(seed):
+    """The same random call shapes with a few key tokens scaled x50, where the attention kernels'
+    negligible-tile tests skip most key tiles of longer calls: the kernels with the tests against
+    the ones without (switched by the threshold hook), and both against the oracle."""
+    from sageattention import _native
+    lib = _native.load()
+    c = _case(500 + seed)
+    c["nq"] = max(c["nq"], 300) * 4                       # long enough for tiles after the dominant keys
+    c["nk"] = c["nq"] if c["causal"] else max(c["nk"], 257) * 4
+    g = torch.Generator().manual_seed(2000 + seed)
+    q = torch.randn(c["b"], c["hq"], c["nq"], c["d"], generator=g).to(c["dtype"])
+    k = torch.randn(c["b"], c["hkv"], c["nk"], c["d"], generator=g)
+    idx = torch.randperm(c["nk"], generator=g)[: max(4, c["nk"] // 100)]
+    k[:, :, idx] *= 50.0
+    k = k.to(c["dtype"])
+    v = torch.randn(c["b"], c["hkv"], c["nk"], c["d"], generator=g).to(c["dtype"])
+    dev = lambda t: (t.transpose(1, 2).contiguous() if c["layout"] == "NHD" else t).cuda()
+    kwargs = dict(tensor_layout=c["layout"], is_causal=c["causal"], sm_scale=c["sm_scale"], smooth_k=c["smooth_k"],
+                  smooth_v=c["smooth_v"], return_lse=c["lse"])
+    if c["int8"] is not None:
+        kwargs["sk1_int8"] = c["int8"]
+    qd, kd, vd = dev(q), dev(k), dev(v)
+    saved, be._ADAPTIVE = be._ADAPTIVE, False
+    try:
+        lib.sage_debug_skip_threshold(0.0)
+        res_off = sageattention.sageattn(qd, kd, vd, **kwargs)
+        off, lse_off = (res_off[0].clone(), res_off[1].clone()) if c["lse"] else (res_off.clone(), None)
+        lib.sage_debug_skip_threshold(-1.0)
+        res_on = sageattention.sageattn(qd, kd, vd, **kwargs)
+        on, lse_on = res_on if c["lse"] else (res_on, None)
+        torch.cuda.synchronize()
+    finally:
+        lib.sage_debug_skip_threshold(-1.0)
+        be._ADAPTIVE = saved
+    assert be.last_status(on, c["b"], c["hq"], c["nq"], c["hkv"], c["nk"]) == 0
+    assert torch.isfinite(on.float()).all()
+    diff = (on.float() - off.float()).abs().max().item()
+    assert diff <= 2.0 ** -8 * max(off.float().abs().max().item(), 1e-3), (c, diff)
+    assert (on != off).float().mean().item() < 1e-3, c
+    if c["lse"]:
+        assert (lse_on - lse_off).abs().max().item() <= 1e-4, c
+    if c["layout"] == "NHD":
+        on = on.transpose(1, 2)
+    want = R.sageattn_oracle(q, k, v, is_causal=c["causal"], sm_scale=c["sm_scale"], smooth_k=c["smooth_k"],
+                             int8=c["int8"], tile=128, smooth_v=c["smooth_v"])
+    e4m3_scores = c["dtype"] == torch.bfloat16 or c["int8"] is False
+    assert R.cosine(on.cpu(), want) >= (0.9995 if e4m3_scores else 0.9999), c
+    assert R.rel_l1(on.cpu(), want) <= (2e-2 if e4m3_scores else 6e-3), c

@@ -61,6 +61,23 @@ def test_dominant_keys(threshold, dtype, causal, n):
     assert abs(R.rel_l1(on, want) - R.rel_l1(off, want)) < 1e-5
 
 
+@pytest.mark.parametrize("shape", [1, 2])
+@pytest.mark.parametrize("dtype,causal", [(torch.float16, False), (torch.float16, True), (torch.bfloat16, False)])
+def test_both_kernel_shapes_skip_alike(threshold, shape, dtype, causal):
+    """The one-tile and the two-tile shape of the kernel carry the same tests: each, forced, agrees
+    with its own plain instantiation on inputs where most tiles are skipped."""
+    lib = _native.load()
+    q, k, v = R.make_inputs(1, 4, 3000, 128, dtype, seed=77, outlier_frac=0.01, device="cuda")
+    lib.sage_debug_tiles_per_cta(shape)
+    try:
+        on, off = _both(threshold, q, k, v, causal)
+    finally:
+        lib.sage_debug_tiles_per_cta(0)
+    ulp = (2.0 ** -10 if dtype == torch.float16 else 2.0 ** -7) * off.float().abs().clamp_min(2.0 ** -14)
+    assert ((on.float() - off.float()).abs() <= ulp).all()
+    assert (on != off).float().mean().item() < 1e-3
+
+
 def test_nothing_is_skipped_without_dominant_keys(threshold):
     q, k, v = R.make_inputs(1, 4, 3000, 128, torch.float16, seed=5, k_bias_std=0.5, device="cuda")
     on, off = _both(threshold, q, k, v, False)
