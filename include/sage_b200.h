@@ -242,6 +242,37 @@ int sage_attention_ex(const void* q, const void* k, const void* v, void* out, fl
 int sage_workspace_layout_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int64_t Nk,
                              size_t offsets[13]);
 
+/* ---- A packed variable-length batch in one call: replaces `sageattn_varlen`
+ * (sageattention/core.py:1444-1558), whose per-block quantisers take `cu_seqlens` and whose kernel
+ * is launched once for the whole batch.  The cumulative lengths stay on the device: nothing is read
+ * back, so the call neither synchronises nor depends on host copies of the lengths.
+ *
+ *   q, out         packed (total_q, Hq, head_dim); k, v packed (total_k, Hkv, head_dim); strides are
+ *                  (token, head) pairs in elements, multiples of 8, last axis contiguous
+ *   cu_seqlens_q/k DEVICE int32 arrays of n_seq + 1 entries, cu[0] = 0, non-decreasing,
+ *                  cu[n_seq] = total_q / total_k; sequence i has cu[i+1] - cu[i] rows
+ *   max_q, max_k   upper bounds of the sequence lengths: they size the workspace
+ *                  (sage_workspace_bytes_ex(n_seq, Hq, Hkv, max_q, max_k)) and the grids.  A
+ *                  sequence longer than the bound is cut off at the bound (its further query rows
+ *                  are not written, its further keys not seen)
+ *   causal         every sequence must have as many keys as queries (max_q == max_k is checked;
+ *                  the per-sequence equality is the caller's promise)
+ * Each sequence is quantised on its own (its own K mean with smooth_k, its own S), exactly as if it
+ * were passed alone to sage_attention_ex: the results are bit-identical to per-sequence calls.
+ * A sequence without queries costs nothing; one with queries and no keys gets rows of zeros.
+ * The kernels run the one-tile shape without the negligible-tile tests.  Status word and errors as
+ * for sage_attention (the layout is sage_workspace_layout_ex(n_seq, Hq, Hkv, max_q, max_k)). */
+int sage_attention_varlen(const void* q, const void* k, const void* v, void* out,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                          void* workspace, size_t workspace_bytes,
+                          int64_t n_seq, int64_t Hq, int64_t Hkv,
+                          int64_t total_q, int64_t total_k, int64_t max_q, int64_t max_k,
+                          int64_t head_dim,
+                          const int64_t q_strides[2], const int64_t k_strides[2],
+                          const int64_t v_strides[2], const int64_t o_strides[2],
+                          int dtype, int qk_mode, int causal, int smooth_k, float sm_scale,
+                          void* stream);
+
 /* Offsets (bytes from `workspace`) of the intermediates sage_attention uses, for callers and
  * tests that want to look at them: order q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status
  * (the status word is a spare word inside the ctrl block, so that one memset clears both).

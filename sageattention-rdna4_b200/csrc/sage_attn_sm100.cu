@@ -285,6 +285,7 @@ struct AttnKArgs {
   float skip_log2;    // FAST kernels: key tiles whose scores all lie this far (exponent domain) below the running maxima are not exponentiated
   unsigned* skipped;  // FAST kernels, optional: receives the number of (warp, key tile) pairs that were skipped
   int32_t* status;
+  const int *cu_q, *cu_k;   // VARLEN kernels: cumulative token counts of the packed batch (B + 1 entries each)
 };
 
 template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -301,7 +302,11 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
 // The kernel.  NQ = 1: grid (ceil(Nq/128), B*Hq), block 384, two CTAs per SM; NQ = 2: grid
 // (ceil(Nq/256), B*Hq), block 640, one CTA per SM.
 // ------------------------------------------------------------------------------------------------
-template <bool INT8, bool CAUSAL, typename OutT, int NQ, bool FAST>
+// VARLEN: a packed batch.  a.Nq, a.N_pad are the capacity of a sequence's slot in the quantised
+// operands, the grid is sized for the longest sequence allowed; each sequence's own lengths and the
+// first row of its output come from cu_q / cu_k, and a CTA whose query tile lies past its
+// sequence's end returns at once.
+template <bool INT8, bool CAUSAL, typename OutT, int NQ, bool FAST, bool VARLEN>
 __global__ void __launch_bounds__(Shape<NQ>::THREADS, Shape<NQ>::CTAS_PER_SM)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                 const __grid_constant__ CUtensorMap tm_v, const AttnKArgs a) {
@@ -326,7 +331,25 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   // Key tiles query tile g visits: all of them, or when causal those up to its diagonal (a causal
   // call has as many key tiles as query tiles; the second tile of the last CTA may not exist, it
   // then repeats the first one's range and stores nothing).  The producer loads the longer range.
-  const int key_tiles = (int)(a.N_pad / TILE);
+  long long Nq_live = a.Nq, Nk_live = a.N, o_first = (bh / a.Hq) * a.o_sb;   // live lengths; first element of this batch entry's output
+  if (VARLEN) {
+    const long long b = bh / a.Hq;
+    const long long q0 = __ldg(a.cu_q + b), k0 = __ldg(a.cu_k + b);
+    Nq_live = min(max((long long)__ldg(a.cu_q + b + 1) - q0, 0LL), a.Nq);
+    Nk_live = min(max((long long)__ldg(a.cu_k + b + 1) - k0, 0LL), a.N);
+    o_first = q0 * a.o_sr;
+    if ((long long)q_tile0 * TILE >= Nq_live) return;       // before any barrier or TMEM column exists
+    if (Nk_live == 0) {                                     // queries without keys: rows of zeros
+      const long long h = bh % a.Hq;
+      for (int i = tid; i < NQ * TILE * (a.D / 2); i += (int)blockDim.x) {
+        const long long row = (long long)q_tile0 * TILE + i / (a.D / 2);
+        if (row < Nq_live)
+          *reinterpret_cast<uint32_t*>(reinterpret_cast<OutT*>(a.out) + o_first + h * a.o_sh + row * a.o_sr + 2 * (i % (a.D / 2))) = 0u;
+      }
+      return;
+    }
+  }
+  const int key_tiles = VARLEN ? (int)((Nk_live + TILE - 1) / TILE) : (int)(a.N_pad / TILE);
   auto tiles_of = [&](int g) { return CAUSAL ? min(q_tile0 + g + 1, key_tiles) : key_tiles; };
   const int n_load = tiles_of(NQ - 1);
 
@@ -462,8 +485,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       const uint32_t t_o = tmem + ((uint32_t)lane_base << 16) + L::tmem_o(g);
       // c_q = f32(f32(sm_scale * log2e) * sq); rows past N get 1 (their scores are all zero)
       const float sl2 = __fmul_rn(a.sm_scale, LOG2E_F);
-      const float cqA = (q_rowA < a.Nq) ? __fmul_rn(sl2, __ldg(a.sq + (size_t)bh * a.Nq + q_rowA)) : 1.f;
-      const float cqB = (q_rowB < a.Nq) ? __fmul_rn(sl2, __ldg(a.sq + (size_t)bh * a.Nq + q_rowB)) : 1.f;
+      const float cqA = (q_rowA < (VARLEN ? Nq_live : a.Nq)) ? __fmul_rn(sl2, __ldg(a.sq + (size_t)bh * a.Nq + q_rowA)) : 1.f;
+      const float cqB = (q_rowB < (VARLEN ? Nq_live : a.Nq)) ? __fmul_rn(sl2, __ldg(a.sq + (size_t)bh * a.Nq + q_rowB)) : 1.f;
       const float2 cqA2 = make_float2(cqA, cqA), cqB2 = make_float2(cqB, cqB);
       float mA = -INFINITY, mB = -INFINITY, lA = 0.f, lB = 0.f;
       bool ok = true;
@@ -613,8 +636,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             }
           }
         } else {
-          if ((long long)(j + 1) * TILE > a.N) {
-            const int live = (int)(a.N - (long long)j * TILE);            // tile-local key >= live is masked
+          if ((long long)(j + 1) * TILE > (VARLEN ? Nk_live : a.N)) {
+            const int live = (int)((VARLEN ? Nk_live : a.N) - (long long)j * TILE);   // tile-local key >= live is masked
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
               const int key = 16 * (i >> 1) + 4 * c + 2 * (i & 1);
@@ -749,18 +772,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
         const long long b = bh / a.Hq, h = bh - b * a.Hq;
         if (a.lse != nullptr && c == 0) {
           // ln sum_k exp(q.k*sm_scale) = ln2 * (c_q*m + log2 l) (+ q.mean*sm_scale with smooth_k)
-          if (q_rowA < a.Nq) {
+          if (q_rowA < (VARLEN ? Nq_live : a.Nq)) {
             float v = (lA > 0.f) ? 0.6931471805599453f * (cqA * mA + log2f(lA)) : -INFINITY;
             if (a.qm != nullptr) v += a.sm_scale * __ldg(a.qm + (size_t)bh * a.Nq + q_rowA);
             a.lse[(size_t)bh * a.Nq + q_rowA] = v;
           }
-          if (q_rowB < a.Nq) {
+          if (q_rowB < (VARLEN ? Nq_live : a.Nq)) {
             float v = (lB > 0.f) ? 0.6931471805599453f * (cqB * mB + log2f(lB)) : -INFINITY;
             if (a.qm != nullptr) v += a.sm_scale * __ldg(a.qm + (size_t)bh * a.Nq + q_rowB);
             a.lse[(size_t)bh * a.Nq + q_rowB] = v;
           }
         }
-        OutT* orowA = reinterpret_cast<OutT*>(a.out) + b * a.o_sb + h * a.o_sh + q_rowA * a.o_sr + 2 * c;
+        OutT* orowA = reinterpret_cast<OutT*>(a.out) + (VARLEN ? o_first : b * a.o_sb) + h * a.o_sh + q_rowA * a.o_sr + 2 * c;
         OutT* orowB = orowA + 8 * a.o_sr;
         const float* vm = (a.vmean != nullptr) ? a.vmean + (size_t)bh_kv * HD + 2 * c : nullptr;
         uint32_t o[64];
@@ -775,8 +798,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
               const float2 mu = __ldg(reinterpret_cast<const float2*>(vm + 8 * i));
               fa0 += mu.x; fa1 += mu.y; fb0 += mu.x; fb1 += mu.y;
             }
-            if (q_rowA < a.Nq) *reinterpret_cast<uint32_t*>(orowA + 8 * i) = pack2<OutT>(fa0, fa1);
-            if (q_rowB < a.Nq) *reinterpret_cast<uint32_t*>(orowB + 8 * i) = pack2<OutT>(fb0, fb1);
+            if (q_rowA < (VARLEN ? Nq_live : a.Nq)) *reinterpret_cast<uint32_t*>(orowA + 8 * i) = pack2<OutT>(fa0, fa1);
+            if (q_rowB < (VARLEN ? Nq_live : a.Nq)) *reinterpret_cast<uint32_t*>(orowB + 8 * i) = pack2<OutT>(fb0, fb1);
           }
         }
       }
@@ -843,10 +866,10 @@ constexpr float SKIP_LOG2_DEFAULT = 40.f;
 static std::atomic<float> g_skip_log2{SKIP_LOG2_DEFAULT};
 void set_skip_log2(float t) { g_skip_log2.store(t < 0.f ? SKIP_LOG2_DEFAULT : t, std::memory_order_relaxed); }
 
-template <bool INT8, bool CAUSAL, typename OutT, int NQ, bool FAST>
+template <bool INT8, bool CAUSAL, typename OutT, int NQ, bool FAST, bool VARLEN = false>
 static cudaError_t launch_inst(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv,
                                const AttnKArgs& ka, dim3 grid, cudaStream_t st) {
-  auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT, NQ, FAST>;
+  auto kern = attn_fwd_kernel<INT8, CAUSAL, OutT, NQ, FAST, VARLEN>;
   using L = Shape<NQ>;
   // the opt-in to more than 48 KB of dynamic shared memory is per device and per instantiation;
   // it is made once (short calls are dominated by host-side work)
@@ -914,17 +937,23 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   bool two = choose_tiles_per_cta((int64_t)q_tiles, (int64_t)bhq, p.causal != 0, sms) == 2;
   const int forced = g_force_tiles_per_cta.load(std::memory_order_relaxed);
   if (forced != 0) two = (forced == 2);
+  // A packed batch runs on the one-tile kernels without the negligible-tile tests: its sequences
+  // differ in length, and the smaller unit of work evens them out.
+  const bool varlen = p.cu_q != nullptr;
+  ka.cu_q = p.cu_q; ka.cu_k = p.cu_k;
+  if (varlen) two = false;
   dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
   // Which of the two sets of kernels: with the negligible-tile tests (the default) or without.
   // The threshold hook at 0 and the caller's `no_fast_path` both select the plain set.
   const float skip = g_skip_log2.load(std::memory_order_relaxed);
-  const bool fast = !p.no_fast_path && skip > 0.f;
+  const bool fast = !p.no_fast_path && skip > 0.f && !varlen;
   ka.skip_log2 = skip;
   ka.skipped = fast ? p.skipped : nullptr;
   const int key = (p.qk_mode == 0 ? 4 : 0) | (p.causal ? 2 : 0) | (p.out_dtype == 0 ? 1 : 0);
   cudaError_t e;
 #define SAGE_LAUNCH(I8, C, T)                                                                          \
-  e = two ? (fast ? launch_inst<I8, C, T, 2, true>(mq, mk, mv, ka, grid, st)                           \
+  e = varlen ? launch_inst<I8, C, T, 1, false, true>(mq, mk, mv, ka, grid, st) :                       \
+      two ? (fast ? launch_inst<I8, C, T, 2, true>(mq, mk, mv, ka, grid, st)                           \
                   : launch_inst<I8, C, T, 2, false>(mq, mk, mv, ka, grid, st))                         \
           : (fast ? launch_inst<I8, C, T, 1, true>(mq, mk, mv, ka, grid, st)                           \
                   : launch_inst<I8, C, T, 1, false>(mq, mk, mv, ka, grid, st))

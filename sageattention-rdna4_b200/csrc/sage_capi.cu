@@ -88,6 +88,14 @@ int check_dims(const Dims& d) {
   return SAGE_OK;
 }
 
+// A packed variable-length batch: device arrays of B + 1 cumulative token counts and the token
+// counts of the packed tensors (null / 0 for a fixed-length call).
+struct Packed {
+  const int32_t *cu_q, *cu_k;
+  int64_t Tq, Tk;
+};
+constexpr Packed kNotPacked = {nullptr, nullptr, 0, 0};
+
 struct Layout {
   size_t q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status, qm, vmean, total;
 };
@@ -122,7 +130,7 @@ int prologue_impl(const void* q, const void* k, const void* v,
                   float* s_fold, float* mean, float* qm, float* vmean, void* ctrl, const Dims& d, int64_t Nk_pad,
                   const int64_t q_strides[3], const int64_t k_strides[3], const int64_t v_strides[3],
                   int dtype, int qk_mode, int smooth_k, void* stream, const char* who,
-                  int32_t* status = nullptr) {
+                  int32_t* status = nullptr, const Packed& pk = kNotPacked) {
   g_err[0] = 0;
   int rc = check_dims(d);
   if (rc) return rc;
@@ -145,6 +153,7 @@ int prologue_impl(const void* q, const void* k, const void* v,
   p.B = d.B; p.H = d.Hkv; p.N = d.Nk; p.N_pad = Nk_pad; p.Hq = d.Hq; p.Nq = d.Nq; p.D = d.D;
   for (int i = 0; i < 3; ++i) { p.q_strides[i] = q_strides[i]; p.k_strides[i] = k_strides[i]; p.v_strides[i] = v_strides[i]; }
   p.dtype = dtype; p.qk_mode = qk_mode; p.smooth_k = smooth_k;
+  p.cu_q = pk.cu_q; p.cu_k = pk.cu_k; p.Tq = pk.Tq; p.Tk = pk.Tk;
   cudaError_t e = sage::launch_prologue(p, reinterpret_cast<cudaStream_t>(stream));
   if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s", who, cudaGetErrorString(e));
   return SAGE_OK;
@@ -154,7 +163,7 @@ int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
               const void* v8t, const float* svp, const float* s_fold, void* out, float* lse, const float* qm,
               const float* vmean, const Dims& d, int64_t Nk_pad, const int64_t o_strides[3],
               int causal, float sm_scale, int out_dtype, int qk_mode, int32_t* status, void* stream,
-              const char* who, unsigned* skipped = nullptr) {
+              const char* who, unsigned* skipped = nullptr, const Packed& pk = kNotPacked) {
   g_err[0] = 0;
   int rc = check_dims(d);
   if (rc) return rc;
@@ -182,6 +191,7 @@ int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
   p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.out_dtype = out_dtype; p.qk_mode = qk_mode;
   p.status = status;
   p.no_fast_path = no_fast_path; p.skipped = skipped;
+  p.cu_q = pk.cu_q; p.cu_k = pk.cu_k;
   const char* why = nullptr;
   cudaError_t e = sage::launch_attention(p, reinterpret_cast<cudaStream_t>(stream), &why);
   if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s (%s)", who, why ? why : "", cudaGetErrorString(e));
@@ -193,7 +203,7 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
                    const int64_t q_strides[3], const int64_t k_strides[3],
                    const int64_t v_strides[3], const int64_t o_strides[3],
                    int dtype, int qk_mode, int causal, int smooth_k, int smooth_v, float sm_scale, void* stream,
-                   const char* who) {
+                   const char* who, const Packed& pk = kNotPacked) {
   g_err[0] = 0;
   int rc = check_dims(d);
   if (rc) return rc;
@@ -202,6 +212,13 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
   const Layout L = carve(d);
   if (workspace_bytes < L.total)
     return fail(SAGE_E_WORKSPACE, "%s: workspace has %zu bytes, needs %zu", who, workspace_bytes, L.total);
+  // what the attention step would refuse is refused before the prologue is launched
+  if (!out) return fail(SAGE_E_ARG, "%s: null pointer argument", who);
+  if (causal && d.Nq != d.Nk) return fail(SAGE_E_ARG, "%s: a causal call needs as many queries as keys", who);
+  if ((rc = check_strides("out", o_strides))) return rc;
+  if (!aligned16(out)) return fail(SAGE_E_ARG, "%s: pointers must be 16-byte aligned", who);
+  if (!(sm_scale > 0.f) || !(sm_scale <= 3.0e38f))
+    return fail(SAGE_E_ARG, "%s: sm_scale must be finite and positive (got %g)", who, (double)sm_scale);
   const int flags = (qk_mode >= 0) ? (qk_mode & SAGE_QK_NO_FAST_PATH) : (((-qk_mode) & SAGE_QK_NO_FAST_PATH));
   if (qk_mode < 0) qk_mode = (dtype == SAGE_BF16) ? SAGE_QK_E4M3 : SAGE_QK_INT8;
   else qk_mode &= ~SAGE_QK_NO_FAST_PATH;
@@ -214,13 +231,13 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
                      reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.sv),
                      reinterpret_cast<float*>(w + L.svp), reinterpret_cast<float*>(w + L.s_fold),
                      reinterpret_cast<float*>(w + L.mean), qm, vmean, w + L.ctrl, d, Nk_pad,
-                     q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, who, status);
+                     q_strides, k_strides, v_strides, dtype, qk_mode, smooth_k, stream, who, status, pk);
   if (rc) return rc;
   return attn_impl(w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,
                    reinterpret_cast<float*>(w + L.sk), w + L.v8t, reinterpret_cast<float*>(w + L.svp),
                    reinterpret_cast<float*>(w + L.s_fold), out, lse, qm, vmean, d, Nk_pad, o_strides,
                    causal, sm_scale, dtype, qk_mode | flags, status, stream, who,
-                   reinterpret_cast<unsigned*>(status) + 3);
+                   reinterpret_cast<unsigned*>(status) + 3, pk);
 }
 
 }  // namespace
@@ -380,6 +397,33 @@ int sage_attention_ex(const void* q, const void* k, const void* v, void* out, fl
   const Dims d = {B, Hq, Hkv, Nq, Nk, head_dim};
   return attention_impl(q, k, v, out, lse, workspace, workspace_bytes, d, q_strides, k_strides, v_strides,
                         o_strides, dtype, qk_mode, causal, smooth_k, smooth_v, sm_scale, stream, "sage_attention_ex");
+}
+
+int sage_attention_varlen(const void* q, const void* k, const void* v, void* out,
+                          const int32_t* cu_seqlens_q, const int32_t* cu_seqlens_k,
+                          void* workspace, size_t workspace_bytes,
+                          int64_t n_seq, int64_t Hq, int64_t Hkv,
+                          int64_t total_q, int64_t total_k, int64_t max_q, int64_t max_k, int64_t head_dim,
+                          const int64_t q_strides[2], const int64_t k_strides[2],
+                          const int64_t v_strides[2], const int64_t o_strides[2],
+                          int dtype, int qk_mode, int causal, int smooth_k, float sm_scale, void* stream) {
+  g_err[0] = 0;
+  if (!cu_seqlens_q || !cu_seqlens_k) return fail(SAGE_E_ARG, "sage_attention_varlen: cu_seqlens pointer is null");
+  if ((reinterpret_cast<uintptr_t>(cu_seqlens_q) | reinterpret_cast<uintptr_t>(cu_seqlens_k)) & 3u)
+    return fail(SAGE_E_ARG, "sage_attention_varlen: cu_seqlens must be 4-byte aligned");
+  if (total_q < 1 || total_k < 1) return fail(SAGE_E_ARG, "sage_attention_varlen: the packed tensors hold no tokens");
+  if (max_q > total_q || max_k > total_k)
+    return fail(SAGE_E_ARG, "sage_attention_varlen: a longest length exceeds the packed token count");
+  if (total_q >= ((int64_t)1 << 31) || total_k >= ((int64_t)1 << 31))
+    return fail(SAGE_E_UNSUPPORTED, "sage_attention_varlen: more than 2^31 - 1 packed tokens");
+  if (!q_strides || !k_strides || !v_strides || !o_strides) return fail(SAGE_E_ARG, "sage_attention_varlen: strides are null");
+  // (batch, head, row) triples for the shared checks; the batch entry is not used by the kernels
+  const int64_t qs[3] = {q_strides[0], q_strides[1], q_strides[0]}, ks[3] = {k_strides[0], k_strides[1], k_strides[0]};
+  const int64_t vs[3] = {v_strides[0], v_strides[1], v_strides[0]}, os[3] = {o_strides[0], o_strides[1], o_strides[0]};
+  const Dims d = {n_seq, Hq, Hkv, max_q, max_k, head_dim};
+  const Packed pk = {cu_seqlens_q, cu_seqlens_k, total_q, total_k};
+  return attention_impl(q, k, v, out, nullptr, workspace, workspace_bytes, d, qs, ks, vs, os, dtype, qk_mode,
+                        causal, smooth_k, 0, sm_scale, stream, "sage_attention_varlen", pk);
 }
 
 }  // extern "C"

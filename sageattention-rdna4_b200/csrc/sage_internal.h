@@ -21,6 +21,13 @@ struct PrologueParams {
   int dtype;      // 0 fp16, 1 bf16
   int qk_mode;    // 0 int8, 1 e4m3
   int smooth_k;
+  // Packed variable-length batch (both null for a fixed-length call): device arrays of B + 1
+  // cumulative token counts.  Sequence b then has cu_q[b+1] - cu_q[b] queries and
+  // cu_k[b+1] - cu_k[b] keys, its rows start at token cu[b] of the packed (tokens, heads, D)
+  // tensors (the batch strides are not used), Nq / N are the largest lengths allowed and size the
+  // outputs, Tq / Tk the token counts of the packed tensors.
+  const int32_t *cu_q, *cu_k;
+  int64_t Tq, Tk;
 };
 
 struct AttnParams {
@@ -41,6 +48,7 @@ struct AttnParams {
   int32_t* status;
   int no_fast_path;                                    // 1: the kernels without the negligible-tile tests
   unsigned* skipped;                                   // optional: (warp, key tile) pairs the fast path skipped
+  const int32_t *cu_q, *cu_k;                          // packed variable-length batch (see PrologueParams); null otherwise
 };
 
 cudaError_t launch_prologue(const PrologueParams& p, cudaStream_t st);

@@ -38,7 +38,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restrict__ partial,
              unsigned* __restrict__ arrivals, long long N, long long H,
-             long long sb, long long sh, long long sr, int nsplit, long long chunk, int D) {
+             long long sb, long long sh, long long sr, int nsplit, long long chunk, int D,
+             const int* __restrict__ cu) {
   __shared__ double red[16][HD];
   __shared__ int s_last;
   allow_successor();                 // one wave: every CTA of this grid is resident
@@ -46,6 +47,11 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
   const int split = blockIdx.x, bh = blockIdx.y;
   const long long b = bh / H, h = bh - b * H;
   const T* base = K + b * sb + h * sh + 8 * c;
+  if (cu != nullptr) {               // packed batch: this sequence's own length and first token
+    const long long s0 = cu[b], s1 = cu[b + 1];
+    N = min(max(s1 - s0, 0LL), N);
+    base = K + s0 * sr + h * sh + 8 * c;
+  }
   const long long n0 = (long long)split * chunk;
   const long long n1 = min(N, n0 + chunk);
 
@@ -78,7 +84,7 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
     __threadfence();
     double tot = 0.0;
     for (int sp = 0; sp < nsplit; ++sp) tot += __ldcg(&partial[((size_t)bh * nsplit + sp) * HD + tid]);
-    mean[(size_t)bh * HD + tid] = (float)(tot / (double)N);
+    mean[(size_t)bh * HD + tid] = (N > 0) ? (float)(tot / (double)N) : 0.f;
   }
 }
 
@@ -106,6 +112,7 @@ struct QuantArgs {
   int32_t* status;                // set non-zero when a wait on a tile load ran out
   int32_t* status2;               // optional second word that receives the same report
   unsigned long long* next_item;  // global work counter (zeroed with the control block)
+  const int *cu_q, *cu_k;         // VARLEN kernels: cumulative token counts of the packed batch (B + 1 entries each)
 };
 
 // rn(x / s) given rc = rn(1/s)
@@ -160,7 +167,11 @@ __device__ __forceinline__ uint32_t i8x4_magic2(float2 ab, float2 cd) {
                      __byte_perm(__float_as_uint(v.x), __float_as_uint(v.y), 0x0040), 0x5410);
 }
 
-template <typename T, bool INT8>
+// VARLEN: a packed batch.  N, N_pad and Nq are then the capacity of a sequence's slot in the outputs
+// (sized for the longest sequence allowed); every sequence has its own length and its own first
+// token in the inputs, read from cu_q / cu_k.  Tiles past a sequence's end are neither loaded nor
+// written (the attention kernel never visits them).
+template <typename T, bool INT8, bool VARLEN>
 __global__ void __launch_bounds__(256, QT_MINBLOCKS)
 quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                      const __grid_constant__ CUtensorMap tm_v, const QuantArgs a) {
@@ -191,6 +202,15 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     else if (it < 2 * items_k + items_q) { const long long j = it - 2 * items_k; which = 0; bh = a.BHq - 1 - j / tiles_q; tile = j % tiles_q; }
     else { const long long j = it - 2 * items_k - items_q; which = 3; bh = a.BHkv - 1 - j / fold_per_head; tile = j % fold_per_head; }
   };
+  // length and first input token of the sequence an item belongs to
+  auto seq_of = [&](int which, long long bh, long long& start) -> long long {
+    if (!VARLEN) { start = 0; return (which == 0) ? a.Nq : a.N; }
+    const long long b = bh / ((which == 0) ? a.Hq : a.H);
+    const int* cu = (which == 0) ? a.cu_q : a.cu_k;
+    const long long s0 = __ldg(cu + b), s1 = __ldg(cu + b + 1);
+    start = s0;
+    return min(max(s1 - s0, 0LL), (which == 0) ? a.Nq : a.N);
+  };
   // Items are handed out through one global counter: a CTA that is held up (by a head's fold, say)
   // simply takes fewer of them.  Thread 0 publishes the item of a stage in s_item and starts its
   // load; past the end it publishes -1 and completes the stage's barrier by hand.  The counter is
@@ -211,7 +231,18 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       return;
     }
     const long long heads = (which == 0) ? a.Hq : a.H;
-    const int b = (int)(bh / heads), h = (int)(bh - (long long)b * heads);
+    int b = (int)(bh / heads);
+    const int h = (int)(bh - (long long)b * heads);
+    long long row = tile * TILE;
+    if (VARLEN) {                      // a tile past the sequence's end is not loaded; the map has one batch entry
+      long long start;
+      if (row >= seq_of(which, bh, start)) {
+        asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar_) : "memory");
+        return;
+      }
+      row += start;
+      b = 0;
+    }
     const CUtensorMap* map = (which == 0) ? &tm_q : (which == 1 ? &tm_k : &tm_v);
     const uint32_t bar = bar0 + 8u * (uint32_t)stage, dst = base + (uint32_t)stage * QT_STAGE_BYTES;
     // the stage was last touched by ordinary loads and stores (V tiles are staged back into it);
@@ -220,7 +251,7 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(QT_STAGE_BYTES) : "memory");
     asm volatile(
         "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
-        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"((int)(tile * TILE)), "r"(h), "r"(b) : "memory");
+        ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"((int)row), "r"(h), "r"(b) : "memory");
   };
 
   if (tid == 0) {
@@ -267,10 +298,14 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     decode(it, which, bh, tile);
     const long long n_base = tile * TILE;
     const uint8_t* st = gbase + (size_t)stage * QT_STAGE_BYTES;
+    long long seq_start;
+    const long long seq_len = seq_of(which == 3 ? 1 : which, bh, seq_start);
+    const bool beyond = VARLEN && which != 3 && n_base >= seq_len;   // nothing was loaded, nothing is written
 
-    if (which == 0) {
+    if (beyond) {
+    } else if (which == 0) {
       // ---------------------------------- Q ----------------------------------
-      const long long N = a.Nq;
+      const long long N = VARLEN ? seq_len : a.Nq;
       float mu[16];
       if (a.qm != nullptr) {
         const long long b = bh / a.Hq, h = bh - b * a.Hq, bh_kv = b * a.H + h / a.group;
@@ -301,10 +336,10 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           w1.x = e4m3x4(y[4].x, y[4].y, y[5].x, y[5].y); w1.y = e4m3x4(y[6].x, y[6].y, y[7].x, y[7].y);
         }
         if (nrow < N) {
-          uint8_t* dst = a.q8 + ((size_t)bh * N + nrow) * HD + 8 * c;
+          uint8_t* dst = a.q8 + ((size_t)bh * a.Nq + nrow) * HD + 8 * c;
           *reinterpret_cast<uint2*>(dst) = w0;
           *reinterpret_cast<uint2*>(dst + 64) = w1;
-          if (c == 0) a.sq[(size_t)bh * N + nrow] = div_const<QDIV>(amax);
+          if (c == 0) a.sq[(size_t)bh * a.Nq + nrow] = div_const<QDIV>(amax);
         }
         if (a.qm != nullptr) {                          // fixed-order fp32 dot product of the raw row
           float d = 0.f;
@@ -313,12 +348,12 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
           d += __shfl_xor_sync(0xffffffffu, d, 4);
           d += __shfl_xor_sync(0xffffffffu, d, 2);
           d += __shfl_xor_sync(0xffffffffu, d, 1);
-          if (c == 0 && nrow < N) a.qm[(size_t)bh * N + nrow] = d;
+          if (c == 0 && nrow < N) a.qm[(size_t)bh * a.Nq + nrow] = d;
         }
       }
     } else if (which == 1) {
       // ---------------------------------- K ----------------------------------
-      const long long N = a.N, N_pad = a.N_pad;
+      const long long N = VARLEN ? seq_len : a.N, N_pad = a.N_pad;
       float2 nmu[8];
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
@@ -376,7 +411,7 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     } else if (which == 2) {
       // ---------------------------------- V ----------------------------------
-      const long long N = a.N, N_pad = a.N_pad;
+      const long long N = VARLEN ? seq_len : a.N, N_pad = a.N_pad;
       float vmu[16];
 #pragma unroll
       for (int e = 0; e < 8; ++e) {
@@ -397,6 +432,7 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
           if (a.vmean) x[e] = live ? __fsub_rn(x[e], vmu[e]) : 0.f;
+          if (VARLEN && !live) x[e] = 0.f;               // the rows behind a packed sequence are its neighbour's
           amax = fmaxf(amax, fabsf(x[e]));
         }
         amax = quarter_warp_max(amax);
@@ -457,7 +493,7 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       // the head's V tiles were drawn; thread 0 still waits, bounded, for their arrivals.
       int done = 1;
       if (tid == 0) {
-        const unsigned want = (unsigned)tiles_k;
+        const unsigned want = VARLEN ? (unsigned)((seq_len + TILE - 1) / TILE) : (unsigned)tiles_k;
         const volatile unsigned* arr = a.arrivals + bh;
         if (*arr != want) {
           const long long t0 = clock64();
@@ -472,12 +508,13 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         break;
       }
       const long long N_pad = a.N_pad;
+      const long long n_fold = VARLEN ? (seq_len + TILE - 1) / TILE * TILE : N_pad;   // rows that were written
       const float S = fmaxf(__uint_as_float(__ldcg(&a.svmax_bits[bh])), 1.0f);
       if (tile == 0 && tid == 0) a.s_fold[bh] = S;
 #pragma unroll
       for (int i = 0; i < FOLD_KEYS / 1024; ++i) {
         const long long nn = tile * FOLD_KEYS + (long long)i * 1024 + 4 * tid;
-        if (nn < N_pad) {              // N_pad is a multiple of 128: whole float4s
+        if (nn < n_fold) {             // a multiple of 128: whole float4s
           const float4 v = __ldcg(reinterpret_cast<const float4*>(a.sv + (size_t)bh * N_pad + nn));
           float4 o;
           o.x = __fmul_rn(__fdiv_rn(v.x, S), F8_MAX); o.y = __fmul_rn(__fdiv_rn(v.y, S), F8_MAX);
@@ -487,7 +524,7 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
       }
     }
     __syncthreads();                   // the stage may be refilled
-    if (which == 2 && tid == 0) {      // this tile's V scales and maximum are published: one release per CTA
+    if (which == 2 && !beyond && tid == 0) {   // this tile's V scales and maximum are published: one release per CTA
       __threadfence();
       atomicAdd(a.arrivals + bh, 1u);
     }
@@ -534,7 +571,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   double* partial = reinterpret_cast<double*>(reinterpret_cast<char*>(p.ctrl) + CtrlHeader::partial_off(bh));
   // SM count and the opt-in to 64 KB of dynamic shared memory: looked up once per device
   static int sm_count[64] = {0};
-  static bool opted_in[64][2] = {{false}};
+  static bool opted_in[64][4] = {{false}};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return e;
@@ -552,7 +589,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     dim3 grid(nsplit, (unsigned)bh);
     kmean_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.k), p.mean, partial, words,
                                           p.N, p.H, p.k_strides[0], p.k_strides[1], p.k_strides[2],
-                                          nsplit, chunk, (int)p.D);
+                                          nsplit, chunk, (int)p.D, p.cu_k);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -562,7 +599,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     dim3 grid(nsplit, (unsigned)bh);
     kmean_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.v), p.vmean, partial, words + 3 * bh,
                                           p.N, p.H, p.v_strides[0], p.v_strides[1], p.v_strides[2],
-                                          nsplit, chunk, (int)p.D);
+                                          nsplit, chunk, (int)p.D, p.cu_k);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -574,6 +611,8 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   a.N = p.N; a.N_pad = p.N_pad; a.H = p.H;
   a.Nq = p.Nq; a.Hq = p.Hq; a.group = p.Hq / p.H; a.BHq = p.B * p.Hq; a.BHkv = bh; a.qm = p.qm;
   a.sub_mean = p.smooth_k ? 1 : 0;
+  a.cu_q = p.cu_q; a.cu_k = p.cu_k;
+  const bool varlen = p.cu_q != nullptr;
   const int64_t tq = (p.Nq + TILE - 1) / TILE, tk = p.N_pad / TILE;
   a.status = reinterpret_cast<int32_t*>(words + CtrlHeader::status_word(bh));
   a.status2 = p.status;
@@ -581,18 +620,28 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   CUtensorMap mq, mk, mv;
   const CUtensorMapDataType dt = (sizeof(T) == 2 && std::is_same<T, __half>::value) ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
                                                                                       : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
-  if (!make_map4(&mq, p.q, dt, p.D, p.Nq, p.Hq, p.B, p.q_strides) ||
-      !make_map4(&mk, p.k, dt, p.D, p.N, p.H, p.B, p.k_strides) ||
-      !make_map4(&mv, p.v, dt, p.D, p.N, p.H, p.B, p.v_strides))
+  if (varlen) {
+    // packed (tokens, heads, D) tensors: one batch entry that holds every token
+    const int64_t qs[3] = {p.q_strides[1], p.q_strides[1], p.q_strides[2]};
+    const int64_t ks[3] = {p.k_strides[1], p.k_strides[1], p.k_strides[2]};
+    const int64_t vs[3] = {p.v_strides[1], p.v_strides[1], p.v_strides[2]};
+    if (!make_map4(&mq, p.q, dt, p.D, p.Tq, p.Hq, 1, qs) || !make_map4(&mk, p.k, dt, p.D, p.Tk, p.H, 1, ks) ||
+        !make_map4(&mv, p.v, dt, p.D, p.Tk, p.H, 1, vs))
+      return cudaErrorInvalidValue;
+  } else if (!make_map4(&mq, p.q, dt, p.D, p.Nq, p.Hq, p.B, p.q_strides) ||
+             !make_map4(&mk, p.k, dt, p.D, p.N, p.H, p.B, p.k_strides) ||
+             !make_map4(&mv, p.v, dt, p.D, p.N, p.H, p.B, p.v_strides))
     return cudaErrorInvalidValue;
   const long long total = 2 * (long long)bh * tk + (long long)a.BHq * tq;
   long long ctas = (long long)sm_count[dev] * QT_MINBLOCKS;
   if (ctas > total) ctas = total;
-  auto kern = (p.qk_mode == 0) ? quant_qkv_kernel<T, true> : quant_qkv_kernel<T, false>;
-  if (!opted_in[dev][p.qk_mode == 0]) {
+  auto kern = varlen ? ((p.qk_mode == 0) ? quant_qkv_kernel<T, true, true> : quant_qkv_kernel<T, false, true>)
+                     : ((p.qk_mode == 0) ? quant_qkv_kernel<T, true, false> : quant_qkv_kernel<T, false, false>);
+  const int which_kern = (p.qk_mode == 0 ? 1 : 0) | (varlen ? 2 : 0);
+  if (!opted_in[dev][which_kern]) {
     e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QT_SMEM_BYTES);
     if (e != cudaSuccess) return e;
-    opted_in[dev][p.qk_mode == 0] = true;
+    opted_in[dev][which_kern] = true;
   }
   return launch_after_predecessor(kern, dim3((unsigned)ctas), dim3(256), QT_SMEM_BYTES, st, mq, mk, mv, a);
 }

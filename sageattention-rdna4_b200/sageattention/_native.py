@@ -50,6 +50,10 @@ SIGNATURES = {
     "sage_attention_ex": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, ctypes.c_size_t, _I64, _I64, _I64, _I64, _I64, _I64,
                                          _S3, _S3, _S3, _S3, ctypes.c_int, ctypes.c_int, ctypes.c_int,
                                          ctypes.c_int, ctypes.c_int, ctypes.c_float, _P]),
+    "sage_attention_varlen": (ctypes.c_int, [_P, _P, _P, _P, _P, _P, _P, ctypes.c_size_t,
+                                             _I64, _I64, _I64, _I64, _I64, _I64, _I64, _I64,
+                                             _S3, _S3, _S3, _S3, ctypes.c_int, ctypes.c_int, ctypes.c_int,
+                                             ctypes.c_int, ctypes.c_float, _P]),
     "sage_status_mirror": (ctypes.c_int, [_P, _P, ctypes.c_int, _P]),
     "sage_debug_tiles_per_cta": (None, [ctypes.c_int]),
     "sage_debug_skip_threshold": (None, [ctypes.c_float]),
@@ -93,6 +97,10 @@ def load():
 
 def strides3(batch: int, head: int, row: int):
     return (ctypes.c_int64 * 3)(int(batch), int(head), int(row))
+
+
+def strides2(token: int, head: int):
+    return (ctypes.c_int64 * 2)(int(token), int(head))
 
 
 def check(rc: int, what: str):

@@ -542,6 +542,102 @@ def sage_call(q, k, v, tensor_layout="HND", is_causal=False, sm_scale=None, smoo
     return out
 
 
+def packed_view_reason(t: torch.Tensor) -> Optional[str]:
+    """Why a packed (tokens, heads, head_dim) tensor cannot be served as it is, or None: the rule of
+    `strided_view_reason` for the two strides a packed tensor has."""
+    if t.dim() != 3:
+        return "rank"
+    if t.stride(2) != 1:
+        return "last_stride"
+    if t.data_ptr() & 15:
+        return "alignment"
+    for s in (t.stride(0), t.stride(1)):
+        if s <= 0 or s % 8 or s > _STRIDE_MAX:
+            return "stride_range"
+    return None
+
+
+def varlen_workspace_bytes(n_seq: int, hq: int, hkv: int, max_q: int, max_k: int) -> int:
+    """Bytes of workspace `sage_call_varlen` takes: every sequence gets a slot sized for the longest."""
+    return int(_native.load().sage_workspace_bytes_ex(n_seq, hq, hkv, max_q, max_k))
+
+
+def sage_call_varlen(q, k, v, cu_q, cu_k, max_q: int, max_k: int, is_causal=False, sm_scale=None,
+                     smooth_k=True, out: Optional[torch.Tensor] = None):
+    """A packed variable-length batch through the single C entry point `sage_attention_varlen`.
+
+    q (total_q, Hq, D), k and v (total_k, Hkv, D); `cu_q` / `cu_k` int32 DEVICE tensors of
+    batch + 1 cumulative lengths, never read on the host: the call does not synchronise.
+    `max_q` / `max_k` bound the sequence lengths and size the workspace.  Returns (total_q, Hq, D).
+    """
+    _counters["calls"] += 1
+    for name, t in (("q", q), ("k", k), ("v", v)):
+        reason = packed_view_reason(t)
+        if reason is not None:
+            _counters["refusals"] += 1
+            raise ValueError("sageattn_varlen (B200 path) cannot serve %s: %s" % (name, reason))
+    if not (q.is_cuda and k.is_cuda and v.is_cuda and cu_q.is_cuda and cu_k.is_cuda):
+        raise ValueError("sageattn_varlen (B200 path) needs CUDA tensors; there is no CPU path")
+    if not (q.device == k.device == v.device == cu_q.device == cu_k.device):
+        raise ValueError("sageattn_varlen (B200 path): tensors on different devices")
+    if q.dtype not in (torch.float16, torch.bfloat16) or k.dtype != q.dtype or v.dtype != q.dtype:
+        raise ValueError("sageattn_varlen (B200 path): q, k, v must share one dtype, fp16 or bf16")
+    if cu_q.dtype != torch.int32 or cu_k.dtype != torch.int32 or not cu_q.is_contiguous() or not cu_k.is_contiguous():
+        raise ValueError("sageattn_varlen (B200 path): cumulative lengths must be contiguous int32")
+    tq, hq, d = (int(x) for x in q.shape)
+    tk, hkv, dk = (int(x) for x in k.shape)
+    if tuple(v.shape) != (tk, hkv, dk) or dk != d or hq % hkv:
+        raise ValueError("sageattn_varlen (B200 path): q, k, v shapes do not fit together")
+    if d % 8 or not (8 <= d <= HEAD_DIM):
+        raise NotImplementedError("sageattn (B200 path) serves head_dim 8..128 in multiples of 8")
+    n_seq = cu_q.numel() - 1
+    if n_seq < 1 or cu_k.numel() != n_seq + 1:
+        raise ValueError("sageattn_varlen (B200 path): cumulative lengths need batch + 1 entries each")
+    max_q, max_k = int(max_q), int(max_k)
+    if not (1 <= max_q <= tq and 1 <= max_k <= tk):
+        raise ValueError("sageattn_varlen (B200 path): max_seqlen outside 1..total tokens")
+    if is_causal and max_q != max_k:
+        raise ValueError("sageattn_varlen (B200 path): a causal call needs q_len == kv_len")
+    scale = d ** -0.5 if sm_scale is None else float(sm_scale)
+    if not (0.0 < scale < float("inf")):
+        raise ValueError("sageattn (B200 path): sm_scale must be finite and positive, got %r" % (sm_scale,))
+    lib = _native.load()
+    dev = q.device
+    if out is None:
+        out = torch.empty((tq, hq, d), dtype=q.dtype, device=dev)
+    elif tuple(out.shape) != (tq, hq, d) or out.dtype != q.dtype or packed_view_reason(out) is not None:
+        raise ValueError("out must have q's shape and dtype and be a servable view")
+    offs = (ctypes.c_size_t * 13)()
+    if lib.sage_workspace_layout_ex(n_seq, hq, hkv, max_q, max_k, offs) != 13:
+        _native.check(-1, "sage_workspace_layout_ex")
+    ws_bytes, status_off = varlen_workspace_bytes(n_seq, hq, hkv, max_q, max_k), int(offs[10])
+    stream_id = torch.cuda.current_stream(dev).cuda_stream
+    st = _state(dev, stream_id)
+    if st.host_word is not None and st.host_word.value:
+        st.raise_if_failed("the next call on the stream")
+    ws = st.ws
+    if ws is None or ws.numel() < ws_bytes:
+        ws = _grow(st, dev, ws_bytes)
+    st.status_off, st.shape = status_off, (n_seq, hq, hkv, max_q, max_k)
+    capturing = torch.cuda.is_current_stream_capturing()
+    watch = _WATCH and not (capturing and st.host_word is None)
+    args = (q.data_ptr(), k.data_ptr(), v.data_ptr(), out.data_ptr(), cu_q.data_ptr(), cu_k.data_ptr(),
+            ws.data_ptr(), ws.numel(), n_seq, hq, hkv, tq, tk, max_q, max_k, d,
+            _native.strides2(q.stride(0), q.stride(1)), _native.strides2(k.stride(0), k.stride(1)),
+            _native.strides2(v.stride(0), v.stride(1)), _native.strides2(out.stride(0), out.stride(1)),
+            _dtype_code(q.dtype), -1, 1 if is_causal else 0, 1 if smooth_k else 0, scale, stream_id)
+    with torch.cuda.device(dev):
+        rc = lib.sage_attention_varlen(*args)
+        if watch and not rc:
+            rc = lib.sage_status_mirror(ws.data_ptr() + status_off, ctypes.addressof(_host_word(st)), 1, stream_id)
+    if rc:
+        _native.check(rc, "sage_attention_varlen")
+    if _STRICT:
+        torch.cuda.current_stream(dev).synchronize()
+        st.raise_if_failed("this call (strict mode)")
+    return out
+
+
 def workspace_views(b: int, h: int, n: int, ws: torch.Tensor, int8: bool) -> Dict[str, torch.Tensor]:
     """Typed views of the intermediates inside a `sage_attention` workspace (for tests/tools)."""
     lib = _native.load()

@@ -145,13 +145,18 @@ def sageattn_varlen(
 
     q : ``[cu_seqlens_q[-1], Hq, D]``; k, v : ``[cu_seqlens_k[-1], Hkv, D]``; ``cu_seqlens_*`` are
     int32 / int64 prefix sums of the sequence lengths (``[batch + 1]``).  Returns
-    ``[cu_seqlens_q[-1], Hq, D]``.  Each run of consecutive sequences with equal lengths is one
-    batched call of the fixed-length kernels on a strided view of the packed tensors (no copies),
-    all on the current stream; the cumulative
-    lengths are read on the host, which synchronises once when they live on the device.
+    ``[cu_seqlens_q[-1], Hq, D]``.
+
+    The batch goes out as ONE call of the kernels, which read the cumulative lengths on the device:
+    with `cu_seqlens_*` on the GPU nothing is read back and the call does not synchronise (the
+    lengths are then the caller's promise; `max_seqlen_q` / `max_seqlen_k` bound them and size the
+    workspace, a longer sequence is cut off at the bound).  Lengths given on the host are checked
+    first, and a batch of equal lengths takes the fixed-length kernels on a strided view.  Only a
+    batch so ragged that slots of the longest length would take more than `_VARLEN_SLOT_FACTOR`
+    times the packed size (and more than `_VARLEN_SLOT_FREE_BYTES`) is split into runs of equal
+    lengths, one call each; that path needs the lengths on the host and copies them if necessary.
     `smooth_k` subtracts each sequence's own K mean (the reference subtracts the mean over the
     whole packed batch; softmax is invariant to either shift, only rounding differs).
-    `max_seqlen_q` / `max_seqlen_k` are checked, not needed.
     """
     _reject_common(False, kwargs)
     if q.dim() != 3 or k.dim() != 3 or v.dim() != 3:
@@ -161,20 +166,41 @@ def sageattn_varlen(
         raise ValueError("cu_seqlens_q and cu_seqlens_k must be 1-D with batch + 1 entries each")
     if cu_seqlens_q.dtype not in (torch.int32, torch.int64) or cu_seqlens_k.dtype not in (torch.int32, torch.int64):
         raise ValueError("cu_seqlens_q and cu_seqlens_k must be int32 or int64")
+    if k.size(0) != v.size(0):
+        raise ValueError("cu_seqlens do not match the packed tensors")
+    n_seq = cu_seqlens_q.numel() - 1
+    max_q, max_k = int(max_seqlen_q), int(max_seqlen_k)
+    if q.size(0) == 0:
+        return torch.empty_like(q)
+    on_device = cu_seqlens_q.is_cuda and cu_seqlens_k.is_cuda
+    one_call = _varlen_slots_fit(n_seq, q.size(1), k.size(1), q.size(0), k.size(0), max_q, max_k)
+    if on_device and one_call:
+        if max_q < 1 or max_k < 1:
+            raise ValueError("max_seqlen_q and max_seqlen_k must be positive")
+        return _be.sage_call_varlen(q, k, v, cu_seqlens_q.to(torch.int32), cu_seqlens_k.to(torch.int32),
+                                    min(max_q, q.size(0)), min(max_k, k.size(0)), is_causal=bool(is_causal),
+                                    sm_scale=sm_scale, smooth_k=bool(smooth_k))
     cq = [int(x) for x in cu_seqlens_q.tolist()]
     ck = [int(x) for x in cu_seqlens_k.tolist()]
-    if cq[0] != 0 or ck[0] != 0 or cq[-1] != q.size(0) or ck[-1] != k.size(0) or k.size(0) != v.size(0):
+    if cq[0] != 0 or ck[0] != 0 or cq[-1] != q.size(0) or ck[-1] != k.size(0):
         raise ValueError("cu_seqlens do not match the packed tensors")
-    for i in range(len(cq) - 1):                      # every sequence is checked before anything is launched
+    for i in range(n_seq):                            # every sequence is checked before anything is launched
         nq, nk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
-        if nq < 0 or nk < 0 or nq > max_seqlen_q or nk > max_seqlen_k:
+        if nq < 0 or nk < 0 or nq > max_q or nk > max_k:
             raise ValueError("sequence %d has lengths (%d, %d) outside 0..max_seqlen" % (i, nq, nk))
         if nq > 0 and nk == 0:
             raise ValueError("sequence %d has queries but no keys" % i)
         if is_causal and nq != nk:
             raise ValueError("sequence %d: a causal call needs q_len == kv_len" % i)
     out = torch.empty_like(q)
-    n_seq = len(cq) - 1
+    uniform = all(cq[i + 1] - cq[i] == cq[1] and ck[i + 1] - ck[i] == ck[1] for i in range(n_seq))
+    if one_call and not uniform:
+        dev = q.device
+        return _be.sage_call_varlen(q, k, v, torch.tensor(cq, dtype=torch.int32).to(dev, non_blocking=True),
+                                    torch.tensor(ck, dtype=torch.int32).to(dev, non_blocking=True),
+                                    max(cq[i + 1] - cq[i] for i in range(n_seq)),
+                                    max(ck[i + 1] - ck[i] for i in range(n_seq)), is_causal=bool(is_causal),
+                                    sm_scale=sm_scale, smooth_k=bool(smooth_k), out=out)
     i = 0
     while i < n_seq:
         nq, nk = cq[i + 1] - cq[i], ck[i + 1] - ck[i]
@@ -188,6 +214,22 @@ def sageattn_varlen(
                           sm_scale=sm_scale, smooth_k=bool(smooth_k), out=out[cq[i]:cq[j]].unflatten(0, (run, nq)))
         i = j
     return out
+
+
+#: A packed batch goes out as one call when slots of the longest length for every sequence take at
+#: most this many times the packed token count, or less than the byte figure below in any case.
+_VARLEN_SLOT_FACTOR = 4
+_VARLEN_SLOT_FREE_BYTES = 1 << 30
+
+
+def _varlen_slots_fit(n_seq: int, hq: int, hkv: int, total_q: int, total_k: int, max_q: int, max_k: int) -> bool:
+    """Whether the one-call form's workspace (a slot of the longest length per sequence) is acceptable."""
+    max_q, max_k = max(1, min(max_q, total_q)), max(1, min(max_k, total_k))
+    slots = n_seq * (hq * max_q + 2 * hkv * max_k)
+    packed = hq * total_q + 2 * hkv * total_k
+    if n_seq * hq > 65535:                            # the grid's (batch, head) axis
+        return False
+    return slots <= _VARLEN_SLOT_FACTOR * packed or slots * 132 <= _VARLEN_SLOT_FREE_BYTES
 
 
 # upstream aliases kept so that existing call sites import unchanged

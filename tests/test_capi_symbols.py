@@ -99,6 +99,35 @@ def test_extended_entry_points_validate_on_the_host():
     assert rc == _native.SAGE_E_ARG and b"padded key length" in lib.sage_last_error()
 
 
+def test_packed_batch_entry_point_validates_on_the_host():
+    """`sage_attention_varlen` refuses bad arguments with a code and a message before touching CUDA."""
+    lib = _native.load()
+    s2 = _native.strides2(512, 128)
+    buf = (ctypes.c_char * 4096)()
+    p = ctypes.c_void_p((ctypes.addressof(buf) + 255) // 256 * 256)
+
+    def call(cu_q=p, cu_k=p, n_seq=3, hq=4, hkv=2, tq=600, tk=700, mq=300, mk=400, d=128, causal=0,
+             ws=p, ws_bytes=1 << 40, strides=s2, scale=0.1):
+        return lib.sage_attention_varlen(p, p, p, p, cu_q, cu_k, ws, ws_bytes, n_seq, hq, hkv, tq, tk, mq, mk, d,
+                                         strides, strides, strides, strides, 0, -1, causal, 1, scale, None)
+
+    assert call(cu_q=None) == _native.SAGE_E_ARG and b"cu_seqlens" in lib.sage_last_error()
+    assert call(cu_k=ctypes.c_void_p(p.value + 2)) == _native.SAGE_E_ARG
+    assert call(tq=0) == _native.SAGE_E_ARG
+    assert call(mq=601) == _native.SAGE_E_ARG and b"longest" in lib.sage_last_error()
+    assert call(tq=1 << 31, mq=300) == _native.SAGE_E_UNSUPPORTED
+    assert call(n_seq=0) == _native.SAGE_E_ARG
+    assert call(hq=3) == _native.SAGE_E_ARG and b"multiple" in lib.sage_last_error()
+    assert call(d=136) == _native.SAGE_E_UNSUPPORTED
+    assert call(strides=_native.strides2(516, 128)) == _native.SAGE_E_ARG          # not a multiple of 8
+    assert call(ws=None) == _native.SAGE_E_ARG
+    assert call(ws_bytes=4096) == _native.SAGE_E_WORKSPACE
+    # the workspace is the fixed-length one for n_seq slots of the longest lengths
+    need = lib.sage_workspace_bytes_ex(3, 4, 2, 300, 400)
+    assert call(ws_bytes=need - 1) == _native.SAGE_E_WORKSPACE
+    assert call(causal=1) == _native.SAGE_E_ARG and b"causal" in lib.sage_last_error()   # 300 != 400
+
+
 def test_attention_shape_rule_is_host_arithmetic():
     """`sage_attention_tiles_per_cta` needs no GPU.  The cases are call sizes on which both shapes
     were timed on a 148-SM part (one-tile / two-tile ms in the comments)."""
