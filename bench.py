@@ -410,6 +410,26 @@ def other_arms(q, k, v, dev, causal_main: bool) -> dict:
     ms = timed(lambda: sageattention.sageattn_varlen(qv, kv, vv, cu, cu, ln, ln, is_causal=causal_main), 3)
     wide["varlen_11x4096"] = dict(ms=ms, tflops=seqs * 4.0 * H * ln * ln * D * (0.5 if causal_main else 1.0)
                                   / (ms * 1e-3) / 1e12)
+    # a ragged packed batch, lengths on the device: one call of the kernels, nothing read back;
+    # beside it the same batch split into per-length calls (the form that needs the lengths on the host)
+    lens = [8192, 1024, 4096, 2048, 6144, 512, 3072, 7168, 1536, 5120, 6144]
+    tot = sum(lens)
+    qv, kv, vv = (t[0, :, :tot].transpose(0, 1).contiguous() for t in (q, k, v))
+    cu_host = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32)
+    cu_dev = cu_host.to(dev)
+    rag_flops = sum(4.0 * H * n * n * D for n in lens) * (0.5 if causal_main else 1.0)
+    ms = timed(lambda: sageattention.sageattn_varlen(qv, kv, vv, cu_dev, cu_dev, max(lens), max(lens),
+                                                     is_causal=causal_main), 3)
+    wide["varlen_ragged_11_sequences_one_call"] = dict(ms=ms, tflops=rag_flops / (ms * 1e-3) / 1e12, tokens=tot)
+    import sageattention.core as _core
+    saved = (_core._VARLEN_SLOT_FACTOR, _core._VARLEN_SLOT_FREE_BYTES)
+    _core._VARLEN_SLOT_FACTOR, _core._VARLEN_SLOT_FREE_BYTES = 0, 0
+    try:
+        ms = timed(lambda: sageattention.sageattn_varlen(qv, kv, vv, cu_host, cu_host, max(lens), max(lens),
+                                                         is_causal=causal_main), 3)
+    finally:
+        _core._VARLEN_SLOT_FACTOR, _core._VARLEN_SLOT_FREE_BYTES = saved
+    wide["varlen_ragged_11_sequences_call_per_length"] = dict(ms=ms, tflops=rag_flops / (ms * 1e-3) / 1e12)
     out["wider_call_shapes"] = wide
     return out
 
@@ -579,6 +599,27 @@ def main() -> int:
     for _ in range(args.warmup):
         out = sageattention.sageattn(q, k, v, is_causal=causal)
     sync_all()
+
+    # ---- the prologue alone, before the GPU has been under the attention kernel for seconds ----
+    # (after that its SM clock sags under the power cap for a while and the quantiser, which keeps the
+    # SMs busy while it streams, reads 1 to 5 % slower; the HBM yardstick was taken on a GPU at rest).
+    # The prologue lasts about half a millisecond: timed call by call from an idle GPU, the host's
+    # launch latency before the first kernel would be counted as kernel time.  So it is timed as a
+    # back-to-back batch (the GPU is still busy with call i when call i+1 is enqueued).
+    pq = be.quant_qkv(q, k, v)
+    for _ in range(3):
+        pq = be.quant_qkv(q, k, v, reuse=pq)
+    torch.cuda.synchronize(dev)
+    time.sleep(0.5)
+    pro_iters = max(args.steps, 20)
+    pe0, pe1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    pe0.record(stream)
+    for _ in range(pro_iters):
+        pq = be.quant_qkv(q, k, v, reuse=pq)
+    pe1.record(stream)
+    torch.cuda.synchronize(dev)
+    pro = pe0.elapsed_time(pe1) / pro_iters
+    sync_all()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     with ClockSampler(physical_gpu_index(local)) as clk:
         e0.record(stream)
@@ -592,7 +633,6 @@ def main() -> int:
     status = be.last_status(q, B, H, N)
 
     # ---- per-kernel durations (same launches through the two reference-shaped entry points) ----
-    pq = be.quant_qkv(q, k, v)
     o2 = torch.empty_like(q)
     st = torch.zeros(1, dtype=torch.int32, device=dev)
     ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
@@ -607,16 +647,6 @@ def main() -> int:
         if i >= args.warmup:
             att_ms.append(ev[1].elapsed_time(ev[2]))
     att = statistics.mean(att_ms)
-    # The prologue lasts about half a millisecond: timed call by call from an idle GPU, the host's
-    # launch latency before the first kernel would be counted as kernel time.  So it is timed as a
-    # back-to-back batch (the GPU is still busy with call i when call i+1 is enqueued).
-    pro_iters = max(args.steps, 20)
-    ev[0].record(stream)
-    for _ in range(pro_iters):
-        pq = be.quant_qkv(q, k, v, reuse=pq)
-    ev[1].record(stream)
-    torch.cuda.synchronize(dev)
-    pro = ev[0].elapsed_time(ev[1]) / pro_iters
     pk = peaks()
     achieved = flops(causal) / (att * 1e-3) / 1e12
     # The yardstick: this GPU's own dense 8-bit rate, measured in this run on rank 0 (the other

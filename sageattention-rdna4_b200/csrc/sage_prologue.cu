@@ -34,7 +34,7 @@ namespace sage {
 // Kernel 1: partial fp64 column sums of K; the last CTA of a head combines them in split order.
 // grid (nsplit, B*H), block 256 = 16 row lanes x 16 column chunks of 8 elements.
 // ------------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, bool VARLEN>
 __global__ void __launch_bounds__(256)
 kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restrict__ partial,
              unsigned* __restrict__ arrivals, long long N, long long H,
@@ -47,7 +47,7 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
   const int split = blockIdx.x, bh = blockIdx.y;
   const long long b = bh / H, h = bh - b * H;
   const T* base = K + b * sb + h * sh + 8 * c;
-  if (cu != nullptr) {               // packed batch: this sequence's own length and first token
+  if (VARLEN) {                      // packed batch: this sequence's own length and first token
     const long long s0 = cu[b], s1 = cu[b + 1];
     N = min(max(s1 - s0, 0LL), N);
     base = K + s0 * sr + h * sh + 8 * c;
@@ -84,7 +84,7 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
     __threadfence();
     double tot = 0.0;
     for (int sp = 0; sp < nsplit; ++sp) tot += __ldcg(&partial[((size_t)bh * nsplit + sp) * HD + tid]);
-    mean[(size_t)bh * HD + tid] = (N > 0) ? (float)(tot / (double)N) : 0.f;
+    mean[(size_t)bh * HD + tid] = (!VARLEN || N > 0) ? (float)(tot / (double)N) : 0.f;
   }
 }
 
@@ -587,9 +587,9 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     long long chunk = (p.N + nsplit - 1) / nsplit;
     chunk = (chunk + 15) / 16 * 16;
     dim3 grid(nsplit, (unsigned)bh);
-    kmean_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.k), p.mean, partial, words,
-                                          p.N, p.H, p.k_strides[0], p.k_strides[1], p.k_strides[2],
-                                          nsplit, chunk, (int)p.D, p.cu_k);
+    auto kmean = p.cu_k ? kmean_kernel<T, true> : kmean_kernel<T, false>;
+    kmean<<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.k), p.mean, partial, words, p.N, p.H,
+                                p.k_strides[0], p.k_strides[1], p.k_strides[2], nsplit, chunk, (int)p.D, p.cu_k);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -597,9 +597,9 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     long long chunk = (p.N + nsplit - 1) / nsplit;
     chunk = (chunk + 15) / 16 * 16;
     dim3 grid(nsplit, (unsigned)bh);
-    kmean_kernel<T><<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.v), p.vmean, partial, words + 3 * bh,
-                                          p.N, p.H, p.v_strides[0], p.v_strides[1], p.v_strides[2],
-                                          nsplit, chunk, (int)p.D, p.cu_k);
+    auto kmean = p.cu_k ? kmean_kernel<T, true> : kmean_kernel<T, false>;
+    kmean<<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.v), p.vmean, partial, words + 3 * bh, p.N, p.H,
+                                p.v_strides[0], p.v_strides[1], p.v_strides[2], nsplit, chunk, (int)p.D, p.cu_k);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
