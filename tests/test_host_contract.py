@@ -126,6 +126,25 @@ def test_varlen_argument_checks():
         sageattention.sageattn_varlen(q, q, q, cu, cu, 6, 6)
 
 
+def test_packed_batch_host_rules():
+    """The two host-side decisions of `sageattn_varlen`: which packed views can be served, and when
+    slots of the longest length per sequence are an acceptable workspace."""
+    from sageattention import core
+    t = _t(10, 2, 128)
+    assert be.packed_view_reason(t) is None
+    assert be.packed_view_reason(t[:, :, ::2]) == "last_stride"
+    assert be.packed_view_reason(t.unsqueeze(0)) == "rank"
+    assert be.packed_view_reason(torch.empty(10, 2, 132, dtype=torch.float16)[:, :, :128]) == "stride_range"
+    fused = _t(10, 3, 2, 128)
+    assert be.packed_view_reason(fused[:, 1]) is None                 # token stride 3 * H * D
+    fit = core._varlen_slots_fit
+    assert fit(11, 8, 8, 11 * 4096, 11 * 4096, 4096, 4096)            # equal lengths: slots == packed size
+    assert fit(4, 8, 8, 1000, 1000, 900, 900)                         # small: below the free allowance
+    assert not fit(4096, 32, 32, 4096 * 64 + 65536, 4096 * 64 + 65536, 65536, 65536)   # one long sequence among thousands
+    assert not fit(40000, 2, 2, 80000, 80000, 4, 4)                   # more (sequence, head) units than a grid axis takes
+    assert fit(3, 2, 2, 10, 10, 10 ** 9, 10 ** 9)                     # bounds above the token count are cut to it
+
+
 def test_pad_len():
     assert [be.pad_len(n) for n in (1, 127, 128, 129, 8771, 47520)] == [128, 128, 128, 256, 8832, 47616]
 
