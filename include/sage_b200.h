@@ -260,6 +260,8 @@ int sage_workspace_layout_ex(int64_t B, int64_t Hq, int64_t Hkv, int64_t Nq, int
  * Each sequence is quantised on its own (its own K mean with smooth_k, its own S), exactly as if it
  * were passed alone to sage_attention_ex: the results are bit-identical to per-sequence calls.
  * A sequence without queries costs nothing; one with queries and no keys gets rows of zeros.
+ * The arrays are not validated (that would need them on the host); the kernels clamp every start
+ * and end to the packed token counts, so that no access leaves q, k, v or out whatever they hold.
  * The kernels run the one-tile shape without the negligible-tile tests.  Status word and errors as
  * for sage_attention (the layout is sage_workspace_layout_ex(n_seq, Hq, Hkv, max_q, max_k)). */
 int sage_attention_varlen(const void* q, const void* k, const void* v, void* out,

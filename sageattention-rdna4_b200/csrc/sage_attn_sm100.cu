@@ -286,6 +286,7 @@ struct AttnKArgs {
   unsigned* skipped;  // FAST kernels, optional: receives the number of (warp, key tile) pairs that were skipped
   int32_t* status;
   const int *cu_q, *cu_k;   // VARLEN kernels: cumulative token counts of the packed batch (B + 1 entries each)
+  long long Tq, Tk;         // VARLEN kernels: tokens in the packed q / out and k / v tensors
 };
 
 template <typename OutT> __device__ __forceinline__ uint32_t pack2(float a, float b);
@@ -334,9 +335,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
   long long Nq_live = a.Nq, Nk_live = a.N, o_first = (bh / a.Hq) * a.o_sb;   // live lengths; first element of this batch entry's output
   if (VARLEN) {
     const long long b = bh / a.Hq;
-    const long long q0 = __ldg(a.cu_q + b), k0 = __ldg(a.cu_k + b);
-    Nq_live = min(max((long long)__ldg(a.cu_q + b + 1) - q0, 0LL), a.Nq);
-    Nk_live = min(max((long long)__ldg(a.cu_k + b + 1) - k0, 0LL), a.N);
+    // clamped to the packed tensors: whatever the arrays hold, no row outside `out` is written
+    const long long q0 = min(max((long long)__ldg(a.cu_q + b), 0LL), a.Tq), k0 = min(max((long long)__ldg(a.cu_k + b), 0LL), a.Tk);
+    Nq_live = min(max(min((long long)__ldg(a.cu_q + b + 1), a.Tq) - q0, 0LL), a.Nq);
+    Nk_live = min(max(min((long long)__ldg(a.cu_k + b + 1), a.Tk) - k0, 0LL), a.N);
     o_first = q0 * a.o_sr;
     if ((long long)q_tile0 * TILE >= Nq_live) return;       // before any barrier or TMEM column exists
     if (Nk_live == 0) {                                     // queries without keys: rows of zeros
@@ -940,7 +942,7 @@ cudaError_t launch_attention(const AttnParams& p, cudaStream_t st, const char** 
   // A packed batch runs on the one-tile kernels without the negligible-tile tests: its sequences
   // differ in length, and the smaller unit of work evens them out.
   const bool varlen = p.cu_q != nullptr;
-  ka.cu_q = p.cu_q; ka.cu_k = p.cu_k;
+  ka.cu_q = p.cu_q; ka.cu_k = p.cu_k; ka.Tq = p.Tq; ka.Tk = p.Tk;
   if (varlen) two = false;
   dim3 grid(two ? (q_tiles + 1) / 2 : q_tiles, (unsigned)bhq);
   // Which of the two sets of kernels: with the negligible-tile tests (the default) or without.

@@ -191,7 +191,7 @@ int attn_impl(const void* q8, const float* sq, const void* k8, const float* sk,
   p.causal = causal ? 1 : 0; p.sm_scale = sm_scale; p.out_dtype = out_dtype; p.qk_mode = qk_mode;
   p.status = status;
   p.no_fast_path = no_fast_path; p.skipped = skipped;
-  p.cu_q = pk.cu_q; p.cu_k = pk.cu_k;
+  p.cu_q = pk.cu_q; p.cu_k = pk.cu_k; p.Tq = pk.Tq; p.Tk = pk.Tk;
   const char* why = nullptr;
   cudaError_t e = sage::launch_attention(p, reinterpret_cast<cudaStream_t>(stream), &why);
   if (e != cudaSuccess) return fail(SAGE_E_CUDA, "%s: %s (%s)", who, why ? why : "", cudaGetErrorString(e));

@@ -49,6 +49,7 @@ struct AttnParams {
   int no_fast_path;                                    // 1: the kernels without the negligible-tile tests
   unsigned* skipped;                                   // optional: (warp, key tile) pairs the fast path skipped
   const int32_t *cu_q, *cu_k;                          // packed variable-length batch (see PrologueParams); null otherwise
+  int64_t Tq, Tk;                                      // with cu_q / cu_k: tokens in the packed tensors
 };
 
 cudaError_t launch_prologue(const PrologueParams& p, cudaStream_t st);

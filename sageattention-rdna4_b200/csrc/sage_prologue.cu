@@ -39,7 +39,7 @@ __global__ void __launch_bounds__(256)
 kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restrict__ partial,
              unsigned* __restrict__ arrivals, long long N, long long H,
              long long sb, long long sh, long long sr, int nsplit, long long chunk, int D,
-             const int* __restrict__ cu) {
+             const int* __restrict__ cu, long long tokens) {
   __shared__ double red[16][HD];
   __shared__ int s_last;
   allow_successor();                 // one wave: every CTA of this grid is resident
@@ -48,7 +48,8 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
   const long long b = bh / H, h = bh - b * H;
   const T* base = K + b * sb + h * sh + 8 * c;
   if (VARLEN) {                      // packed batch: this sequence's own length and first token
-    const long long s0 = cu[b], s1 = cu[b + 1];
+    // whatever the arrays hold, nothing outside the packed tokens is read
+    const long long s0 = min(max((long long)cu[b], 0LL), tokens), s1 = min((long long)cu[b + 1], tokens);
     N = min(max(s1 - s0, 0LL), N);
     base = K + s0 * sr + h * sh + 8 * c;
   }
@@ -113,6 +114,7 @@ struct QuantArgs {
   int32_t* status2;               // optional second word that receives the same report
   unsigned long long* next_item;  // global work counter (zeroed with the control block)
   const int *cu_q, *cu_k;         // VARLEN kernels: cumulative token counts of the packed batch (B + 1 entries each)
+  long long Tq, Tk;               // VARLEN kernels: tokens in the packed q and k/v tensors
 };
 
 // rn(x / s) given rc = rn(1/s)
@@ -207,7 +209,9 @@ quant_qkv_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (!VARLEN) { start = 0; return (which == 0) ? a.Nq : a.N; }
     const long long b = bh / ((which == 0) ? a.Hq : a.H);
     const int* cu = (which == 0) ? a.cu_q : a.cu_k;
-    const long long s0 = __ldg(cu + b), s1 = __ldg(cu + b + 1);
+    // clamped to the packed tensor: whatever the arrays hold, a sequence lies inside it
+    const long long T = (which == 0) ? a.Tq : a.Tk;
+    const long long s0 = min(max((long long)__ldg(cu + b), 0LL), T), s1 = min((long long)__ldg(cu + b + 1), T);
     start = s0;
     return min(max(s1 - s0, 0LL), (which == 0) ? a.Nq : a.N);
   };
@@ -589,7 +593,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     dim3 grid(nsplit, (unsigned)bh);
     auto kmean = p.cu_k ? kmean_kernel<T, true> : kmean_kernel<T, false>;
     kmean<<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.k), p.mean, partial, words, p.N, p.H,
-                                p.k_strides[0], p.k_strides[1], p.k_strides[2], nsplit, chunk, (int)p.D, p.cu_k);
+                                p.k_strides[0], p.k_strides[1], p.k_strides[2], nsplit, chunk, (int)p.D, p.cu_k, p.Tk);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -599,7 +603,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     dim3 grid(nsplit, (unsigned)bh);
     auto kmean = p.cu_k ? kmean_kernel<T, true> : kmean_kernel<T, false>;
     kmean<<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.v), p.vmean, partial, words + 3 * bh, p.N, p.H,
-                                p.v_strides[0], p.v_strides[1], p.v_strides[2], nsplit, chunk, (int)p.D, p.cu_k);
+                                p.v_strides[0], p.v_strides[1], p.v_strides[2], nsplit, chunk, (int)p.D, p.cu_k, p.Tk);
     e = cudaGetLastError();
     if (e != cudaSuccess) return e;
   }
@@ -611,7 +615,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
   a.N = p.N; a.N_pad = p.N_pad; a.H = p.H;
   a.Nq = p.Nq; a.Hq = p.Hq; a.group = p.Hq / p.H; a.BHq = p.B * p.Hq; a.BHkv = bh; a.qm = p.qm;
   a.sub_mean = p.smooth_k ? 1 : 0;
-  a.cu_q = p.cu_q; a.cu_k = p.cu_k;
+  a.cu_q = p.cu_q; a.cu_k = p.cu_k; a.Tq = p.Tq; a.Tk = p.Tk;
   const bool varlen = p.cu_q != nullptr;
   const int64_t tq = (p.Nq + TILE - 1) / TILE, tk = p.N_pad / TILE;
   a.status = reinterpret_cast<int32_t*>(words + CtrlHeader::status_word(bh));

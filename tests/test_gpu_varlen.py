@@ -164,3 +164,34 @@ def test_queries_without_keys_get_zeros_and_long_sequences_are_cut():
                                   v[:200].unsqueeze(0).contiguous(), tensor_layout="NHD")
     assert torch.equal(out[:200], want[0])
     assert (out[200:] == 7.0).all()
+
+
+def test_lengths_that_point_outside_the_packed_tensors_are_clamped():
+    """The device-side lengths are the caller's promise, but the kernels keep every access inside
+    the packed tensors whatever the arrays hold: starts and ends are clamped to the token counts.
+    The output sits in the middle of a guarded buffer; the guards must stay untouched, and the
+    sequences that are described correctly come out as usual."""
+    lens = [120, 200, 80]
+    q, k, v = _packed(lens, lens, 2, 2, torch.float16, seed=37)
+    total = sum(lens)
+    guard = 4096
+    buf = torch.full((guard + total * 2 * 128 + guard,), 3.0, dtype=torch.float16, device="cuda")
+    out = buf[guard: guard + total * 2 * 128].view(total, 2, 128)
+    good = _cu(lens)
+    want = sageattention.sageattn_varlen(q, k, v, good, good, 200, 200).clone()
+    for bad in ([0, 120, 10 ** 9, 400],          # an end far beyond the tensor
+                [0, -50, 320, 400],              # a negative entry
+                [0, 500, 320, 400],              # a start beyond the tensor, then a decreasing entry
+                [2 ** 31 - 1, 2 ** 31 - 1, 2 ** 31 - 1, 2 ** 31 - 1]):
+        buf.fill_(3.0)
+        cu = torch.tensor(bad, dtype=torch.int32, device="cuda")
+        be.sage_call_varlen(q, k, v, cu, cu, 200, 200, out=out)
+        torch.cuda.synchronize()
+        assert (buf[:guard] == 3.0).all() and (buf[-guard:] == 3.0).all()
+    # a batch whose last sequence is described wrongly still serves the first two
+    buf.fill_(3.0)
+    cu = torch.tensor([0, 120, 320, 10 ** 9], dtype=torch.int32, device="cuda")
+    be.sage_call_varlen(q, k, v, cu, cu, 200, 200, out=out)
+    torch.cuda.synchronize()
+    assert torch.equal(out[:320], want[:320])
+    assert (buf[:guard] == 3.0).all() and (buf[-guard:] == 3.0).all()
