@@ -370,6 +370,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
       mbar_init(bar(BAR_PV + BAR_PER_TILE * g), 1);
     }
     misc[1] = (*reinterpret_cast<volatile int32_t*>(a.status) != 0) ? 1u : 0u;
+    if (FAST) { misc[4] = 0u; misc[5] = 0u; misc[6] = 0u; misc[7] = 0u; }   // skipped-warp counts, see the MMA issuer
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -452,7 +453,19 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
             ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(jj / L::V_STAGES) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
             if (ok) ok = mbar_wait(bar(BAR_PF + gb), (uint32_t)jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
             if (!ok) break;
+            // FAST kernels: a warp that skips a tile counts itself before it arrives at the P
+            // barrier.  When all eight warps of the query tile did, P(jj) is all zeros and the
+            // product is not issued; the two commits still release the V stage and complete the
+            // P.V barrier (the first tile is never skipped, so the accumulator is initialised).
+            bool all_zero = false;
+            if (FAST) {
+              volatile uint32_t* cnt = misc + 4 + 2 * g + (jj & 1);
+              const uint32_t c8 = *cnt;
+              if (c8 != 0u) *cnt = 0u;
+              all_zero = (c8 == 8u);
+            }
             tc_fence_after();
+            if (!all_zero)
 #pragma unroll
             for (int k = 0; k < 4; ++k)
               mma_ss<false>(tmem + L::tmem_o(g),
@@ -533,6 +546,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           if (!__all_sync(0xffffffffu, w)) return false;
           tc_fence_after();
         }
+        // (after the wait: P.V(j-1) complete means the MMA thread has read and cleared the count of tile j-2)
+        if (lane == 0) atomicAdd(const_cast<uint32_t*>(misc) + 4 + 2 * g + (j & 1), 1u);
         fence_async_smem();
         tc_fence_before();
         __syncwarp();
