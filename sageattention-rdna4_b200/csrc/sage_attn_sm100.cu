@@ -7,16 +7,26 @@
 //            nearly empty round (see launch_attention).
 //   NQ = 2   two neighbouring query tiles of a head per CTA, 640 threads, one CTA per SM: each K
 //            and V^T tile is loaded once for both, each query tile has its own softmax warps,
-//            TMEM columns, P tiles and MMA-issuing thread.  (Causal: the second tile
+//            TMEM columns, P tiles and MMA-issuing threads.  (Causal: the second tile
 //            visits one key tile more than the first.)
-// Both shapes compute every row with the same instructions in the same order.  Roles inside a CTA:
-//   warp 0     TMA producer: the Q tile(s) once, then a 2-deep ring of K tiles (each carrying that
+// Both shapes compute every row with the same instructions in the same order.  Roles inside a CTA
+// with one query tile:
+//   warp 0     TMA producer: the Q tile once, then a 2-deep ring of K tiles (each carrying that
 //              tile's 128 K scales and 128 staged V factors into a 4-slot ring) and the V^T tiles
-//              (a 2-deep ring; a single stage for NQ = 1, whose shared memory holds the second P
-//              tile instead)
-//   warp 1     allocates 256 x NQ TMEM columns; one thread issues the tcgen05.mma of query tile 0
-//   warp 2     NQ = 2: one thread issues the tcgen05.mma of query tile 1 (idle for NQ = 1)
-//   warp 3     idle: it completes the first warpgroup, whose registers setmaxnreg hands over
+//              (a single stage; the shared memory of a second one holds the second P tile)
+//   warp 1     allocates the TMEM columns; one thread issues every tcgen05.mma
+//   warps 2, 3 idle: they complete the first warpgroup, whose registers setmaxnreg hands over
+// and with two query tiles (256 x 2 TMEM columns, 2-deep rings of K and of V^T tiles), where the
+// four product streams of a key tile are spread over the four schedulers of the SM -- issuing a
+// tcgen05.mma or a commit holds up the issuing warp's scheduler, and the softmax warps of the most
+// loaded scheduler set the CTA's pace:
+//   warp 0     loads the Q tiles, then issues Q.K^T of query tile 0
+//   warp 1     issues Q.K^T of query tile 1 and, behind each, loads the K tile two ahead (with its
+//              scale rows) once both tiles' products on that stage have completed
+//   warp 2     issues P.V of query tile 0
+//   warp 3     issues P.V of query tile 1 and, behind each, loads the V^T tile two ahead
+//              (the loads ride with query tile 1 because it runs behind tile 0: its threads would
+//              wait for tile 0's product anyway, tile 0's threads would wait for tile 1's)
 //   warps 4-11 (and 12-19 for the second query tile) softmax: a warp owns 16 query rows (TMEM
 //              lanes) and all 128 key columns, read with the 16-lane 16x256b shape: four threads
 //              share a row, each holds two rows, and a row maximum is two shuffles
@@ -394,8 +404,97 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
     if (warp < 4) {
       asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(L::REGS_PRODUCER));
     }
-    if (warp == 0) {
-      // ------------------------------- TMA producer -------------------------------
+    if (NQ == 2 && warp < 4) {
+      // Two query tiles: the four product streams of a key tile go to the four warps of this
+      // warpgroup, one per scheduler (issuing tcgen05.mma and commits holds up the issuing warp's
+      // scheduler, and the softmax warps on the most loaded scheduler set the pace).  There is no
+      // separate producer: the threads of query tile 1, which runs behind tile 0, also load the
+      // next K tile (after their Q.K^T) and the next V tile (after their P.V), when both tiles'
+      // products on the stage have completed.
+      if (lane == 0) {
+        const int g = warp & 1, gb = BAR_PER_TILE * g;
+        const int n_tiles = tiles_of(g);
+        bool ok = true;
+        if (warp < 2) {
+          // ------------------------------- Q.K^T issuers ---------------------------
+          constexpr uint32_t IDESC_QK = INT8 ? IDESC_I8 : IDESC_F8;
+          const float* sk_row = a.sk + (size_t)bh_kv * a.N_pad;
+          const float* sv_row = a.svp + (size_t)bh_kv * a.N_pad;
+          auto load_k = [&](int j) -> bool {
+            const int s = j & 1;
+            const uint32_t par = ((uint32_t)(j >> 1) & 1u) ^ 1u;
+            if (!mbar_wait(bar(BAR_KE + s), par, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) return false;
+            mbar_expect_tx(bar(BAR_KF + s), TILE_BYTES + 2 * VEC_BYTES);
+            tma_load_3d(base + OFF_K + s * TILE_BYTES, &tm_k, bar(BAR_KF + s), 0, j * TILE, bh_kv);
+            bulk_load(base + OFF_SK + (j & 3) * VEC_BYTES, sk_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
+            bulk_load(base + OFF_SV + (j & 3) * VEC_BYTES, sv_row + (size_t)j * TILE, VEC_BYTES, bar(BAR_KF + s));
+            return true;
+          };
+          if (warp == 0) {
+            prefetch_map(&tm_q); prefetch_map(&tm_k); prefetch_map(&tm_v);
+            mbar_expect_tx(bar(BAR_Q), NQ * TILE_BYTES);
+            for (int t = 0; t < NQ; ++t)                        // rows past the last query arrive as zeros
+              tma_load_3d(base + OFF_Q + t * TILE_BYTES, &tm_q, bar(BAR_Q), 0, (q_tile0 + t) * TILE, bh);
+          } else {
+            ok = load_k(0);
+            if (ok && n_load > 1) ok = load_k(1);
+          }
+          if (ok) ok = mbar_wait(bar(BAR_Q), 0, cta_abort, a.status, ST_TIMEOUT_MMA);
+          for (int j = 0; ok && j < n_tiles; ++j) {
+            const int s = j & 1;
+            ok = mbar_wait(bar(BAR_KF + s), (uint32_t)(j >> 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok && j > 0) ok = mbar_wait(bar(BAR_SFREE + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (!ok) break;
+            tc_fence_after();
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_ss<INT8>(tmem + L::tmem_s(g), kmajor_sw128_desc(base + OFF_Q + g * TILE_BYTES + 32 * k),
+                           kmajor_sw128_desc(base + OFF_K + s * TILE_BYTES + 32 * k), IDESC_QK, k > 0);
+            tc_commit(bar(BAR_KE + s));
+            tc_commit(bar(BAR_SF + gb));
+            if (warp == 1 && j + 2 < n_load) ok = load_k(j + 2);
+          }
+        } else {
+          // ------------------------------- P.V issuers -----------------------------
+          auto load_v = [&](int j) -> bool {
+            const int sv = j % L::V_STAGES;
+            const uint32_t parv = ((uint32_t)(j / L::V_STAGES) & 1u) ^ 1u;
+            if (!mbar_wait(bar(BAR_VE + sv), parv, cta_abort, a.status, ST_TIMEOUT_PRODUCER)) return false;
+            mbar_expect_tx(bar(BAR_VF + sv), TILE_BYTES);
+            tma_load_3d(base + OFF_V + sv * TILE_BYTES, &tm_v, bar(BAR_VF + sv), j * TILE, 0, bh_kv);
+            return true;
+          };
+          if (warp == 3) {
+            for (int j = 0; ok && j < L::V_STAGES && j < n_load; ++j) ok = load_v(j);
+          }
+          for (int jj = 0; ok && jj < n_tiles; ++jj) {
+            const int s = jj % L::V_STAGES;
+            ok = mbar_wait(bar(BAR_VF + s), (uint32_t)(jj / L::V_STAGES) & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (ok) ok = mbar_wait(bar(BAR_PF + gb), (uint32_t)jj & 1u, cta_abort, a.status, ST_TIMEOUT_MMA);
+            if (!ok) break;
+            bool all_zero = false;
+            if (FAST) {
+              volatile uint32_t* cnt = misc + 4 + 2 * g + (jj & 1);
+              const uint32_t c8 = *cnt;
+              if (c8 != 0u) *cnt = 0u;
+              all_zero = (c8 == 8u);
+            }
+            tc_fence_after();
+            if (!all_zero)
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              mma_ss<false>(tmem + L::tmem_o(g),
+                            kmajor_nosw_desc(base + OFF_P + (g * L::P_BUFS + (jj & (L::P_BUFS - 1))) * TILE_BYTES + 256 * k),
+                            kmajor_sw128_desc(base + OFF_V + s * TILE_BYTES + 32 * k), IDESC_F8,
+                            (jj > 0 || k > 0) ? 1u : 0u);
+            tc_commit(bar(BAR_VE + s));
+            tc_commit(bar(BAR_PV + gb));
+            if (warp == 3 && jj + L::V_STAGES < n_load) ok = load_v(jj + L::V_STAGES);
+          }
+        }
+      }
+    } else if (warp == 0) {
+      // ------------------------------- TMA producer (one query tile per CTA) ------
       if (lane == 0) {
         prefetch_map(&tm_q); prefetch_map(&tm_k); prefetch_map(&tm_v);
         mbar_expect_tx(bar(BAR_Q), NQ * TILE_BYTES);
@@ -426,9 +525,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           tma_load_3d(base + OFF_V + sv * TILE_BYTES, &tm_v, bar(BAR_VF + sv), j * TILE, 0, bh_kv);
         }
       }
-    } else if (warp == 1 || (NQ == 2 && warp == 2)) {
-      // ------------------------------- MMA issuer (one per query tile) ------------
-      const int g = warp - 1;
+    } else if (warp == 1) {
+      // ------------------------------- MMA issuer (one query tile per CTA) --------
+      const int g = 0;
       const int gb = BAR_PER_TILE * g;
       const int n_tiles = tiles_of(g);
       if (lane == 0) {
