@@ -847,11 +847,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           ok = mbar_wait(bar(BAR_PV + gb), (uint32_t)(j - 1) & 1u, cta_abort, a.status, ST_TIMEOUT_SOFTMAX);
           ok = __all_sync(0xffffffffu, ok);
           if (!ok) break;
+          tc_fence_after();
         }
         if (rescale) {
           const float2 aA2 = make_float2(alphaA, alphaA), aB2 = make_float2(alphaB, alphaB);
           uint32_t o[64];
-          tc_fence_after();                                 // (only here does a tcgen05 operation follow the wait)
           tmem_ld_16x256b_x16(t_o, o);
           tmem_ld_wait();
 #pragma unroll
@@ -863,9 +863,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant_
           }
           tmem_st_16x256b_x16(t_o, o);
           tmem_st_wait();
-          tc_fence_before();
         }
         fence_async_smem();
+        tc_fence_before();
         __syncwarp();
         mbar_arrive_lane0(bar(BAR_PF + gb), lane);
       }
