@@ -86,7 +86,7 @@ size_t sage_prologue_ctrl_bytes(int64_t B, int64_t H, int64_t N);
  * Alignment: q, k, v, q8, k8, v8t, sk, sv, svp and ctrl (and vmean of sage_prologue_ex) are read or
  * written with 16-byte vector accesses and must be 16-byte aligned; a misaligned one is refused
  * with SAGE_E_ARG before anything is launched.  sq, s_fold, mean and qm need 4-byte alignment.
- * Two kernel launches (mean, quantise) and one small memset. */
+ * Three kernel launches (a one-block kernel that clears the control words, mean, quantise). */
 int sage_prologue(const void* q, const void* k, const void* v,
                   void* q8, float* sq, void* k8, float* sk, void* v8t, float* sv, float* svp,
                   float* s_fold, float* mean, void* ctrl,
@@ -277,7 +277,7 @@ int sage_attention_varlen(const void* q, const void* k, const void* v, void* out
 
 /* Offsets (bytes from `workspace`) of the intermediates sage_attention uses, for callers and
  * tests that want to look at them: order q8, sq, k8, sk, v8t, sv, svp, s_fold, mean, ctrl, status
- * (the status word is a spare word inside the ctrl block, so that one memset clears both).
+ * (the status word is a spare word inside the ctrl block, so that one clearing kernel clears both).
  * Returns the number of entries written (11). */
 int sage_workspace_layout(int64_t B, int64_t H, int64_t N, size_t offsets[11]);
 

@@ -117,7 +117,7 @@ Layout carve(const Dims& d) {
   L.mean = take(bhk * sage::HD * 4);
   L.ctrl = take(sage::prologue_ctrl_bytes(d.B, d.Hkv, d.Nk));
   // the attention kernel's status word is the spare word of the control header, so that the
-  // prologue's one memset clears it too
+  // prologue's clearing kernel clears it too
   L.status = L.ctrl + 4 * (sage::CtrlHeader::status_word((int64_t)bhk) + 1);
   L.qm = take(bhq * nq * 4);
   L.vmean = take(bhk * sage::HD * 4);
@@ -224,7 +224,7 @@ int attention_impl(const void* q, const void* k, const void* v, void* out, float
   else qk_mode &= ~SAGE_QK_NO_FAST_PATH;
   char* w = reinterpret_cast<char*>(workspace);
   const int64_t Nk_pad = sage_pad_len(d.Nk);
-  int32_t* status = reinterpret_cast<int32_t*>(w + L.status);     // zeroed by the prologue's memset
+  int32_t* status = reinterpret_cast<int32_t*>(w + L.status);     // zeroed by the prologue's clearing kernel
   float* qm = (lse && smooth_k) ? reinterpret_cast<float*>(w + L.qm) : nullptr;
   float* vmean = smooth_v ? reinterpret_cast<float*>(w + L.vmean) : nullptr;
   rc = prologue_impl(q, k, v, w + L.q8, reinterpret_cast<float*>(w + L.sq), w + L.k8,

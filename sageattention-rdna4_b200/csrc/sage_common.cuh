@@ -16,7 +16,7 @@ constexpr float F8_MAX = 448.0f;
 constexpr float SCALE_FLOOR = 1e-12f;
 constexpr float LOG2E_F = 1.4426950408889634f;
 
-// Control block of the prologue (device memory, zeroed by a memset at the start of every call).
+// Control block of the prologue (device memory, zeroed by a small kernel at the start of every call).
 struct CtrlHeader {
   // per head: [0] arrivals of the K mean kernel, [1] V tiles quantised so far, [2] max V scale bits, [3] arrivals
   // of the V mean kernel (smooth_v), laid out as four arrays of BH words; then one status word
@@ -24,7 +24,7 @@ struct CtrlHeader {
   // work counter; the fp64 partial sums (shared by the two mean launches, which run one after the
   // other) follow at `partial_off`.
   // (four more words follow the work counter: the attention kernel's count of skipped
-  // (warp, key tile) pairs, then three spare words; all of them are cleared by the same memset)
+  // (warp, key tile) pairs, then three spare words; all of them are cleared by the same kernel)
   static __host__ __device__ inline size_t words(int64_t bh) { return (size_t)4 * (size_t)bh + 8; }
   static __host__ __device__ inline size_t status_word(int64_t bh) { return (size_t)4 * (size_t)bh; }
   static __host__ __device__ inline size_t partial_off(int64_t bh) {

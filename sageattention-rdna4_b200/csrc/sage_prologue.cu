@@ -31,6 +31,18 @@
 namespace sage {
 
 // ------------------------------------------------------------------------------------------------
+// Kernel 0: clears the control words (arrival counters, running maxima, status words, work and
+// skip counters) of a call.  A kernel rather than a memset so that it and the mean kernel behind it
+// can be launched as programmatic dependents: their CTAs are placed while the kernel before them
+// on the stream drains, and the stream has no memset node to serialise on.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) clear_ctrl_kernel(unsigned* __restrict__ words, int n) {
+  wait_for_predecessor();            // an earlier call may still be using these words
+  allow_successor();
+  for (int i = threadIdx.x; i < n; i += 256) words[i] = 0u;
+}
+
+// ------------------------------------------------------------------------------------------------
 // Kernel 1: partial fp64 column sums of K; the last CTA of a head combines them in split order.
 // grid (nsplit, B*H), block 256 = 16 row lanes x 16 column chunks of 8 elements.
 // ------------------------------------------------------------------------------------------------
@@ -42,6 +54,7 @@ kmean_kernel(const T* __restrict__ K, float* __restrict__ mean, double* __restri
              const int* __restrict__ cu, long long tokens) {
   __shared__ double red[16][HD];
   __shared__ int s_last;
+  wait_for_predecessor();            // the cleared arrival counters
   allow_successor();                 // one wave: every CTA of this grid is resident
   const int tid = threadIdx.x, c = tid & 15, r = tid >> 4;
   const int split = blockIdx.x, bh = blockIdx.y;
@@ -584,7 +597,7 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     e = cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev);
     if (e != cudaSuccess) return e;
   }
-  e = cudaMemsetAsync(p.ctrl, 0, CtrlHeader::words(bh) * 4, st);
+  e = launch_after_predecessor(clear_ctrl_kernel, dim3(1), dim3(256), 0, st, words, (int)CtrlHeader::words(bh));
   if (e != cudaSuccess) return e;
   const int nsplit = std::min(kmean_splits(bh, p.N, sm_count[dev]), kmean_splits_max(bh, p.N));
   if (p.smooth_k) {
@@ -592,9 +605,9 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     chunk = (chunk + 15) / 16 * 16;
     dim3 grid(nsplit, (unsigned)bh);
     auto kmean = p.cu_k ? kmean_kernel<T, true> : kmean_kernel<T, false>;
-    kmean<<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.k), p.mean, partial, words, p.N, p.H,
-                                p.k_strides[0], p.k_strides[1], p.k_strides[2], nsplit, chunk, (int)p.D, p.cu_k, p.Tk);
-    e = cudaGetLastError();
+    e = launch_after_predecessor(kmean, grid, dim3(256), 0, st, reinterpret_cast<const T*>(p.k), p.mean, partial, words,
+                                 (long long)p.N, (long long)p.H, (long long)p.k_strides[0], (long long)p.k_strides[1],
+                                 (long long)p.k_strides[2], nsplit, chunk, (int)p.D, p.cu_k, (long long)p.Tk);
     if (e != cudaSuccess) return e;
   }
   if (p.vmean) {
@@ -602,9 +615,9 @@ static cudaError_t launch_typed(const PrologueParams& p, cudaStream_t st) {
     chunk = (chunk + 15) / 16 * 16;
     dim3 grid(nsplit, (unsigned)bh);
     auto kmean = p.cu_k ? kmean_kernel<T, true> : kmean_kernel<T, false>;
-    kmean<<<grid, 256, 0, st>>>(reinterpret_cast<const T*>(p.v), p.vmean, partial, words + 3 * bh, p.N, p.H,
-                                p.v_strides[0], p.v_strides[1], p.v_strides[2], nsplit, chunk, (int)p.D, p.cu_k, p.Tk);
-    e = cudaGetLastError();
+    e = launch_after_predecessor(kmean, grid, dim3(256), 0, st, reinterpret_cast<const T*>(p.v), p.vmean, partial, words + 3 * bh,
+                                 (long long)p.N, (long long)p.H, (long long)p.v_strides[0], (long long)p.v_strides[1],
+                                 (long long)p.v_strides[2], nsplit, chunk, (int)p.D, p.cu_k, (long long)p.Tk);
     if (e != cudaSuccess) return e;
   }
   QuantArgs a;

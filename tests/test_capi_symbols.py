@@ -38,7 +38,7 @@ def test_host_only_entry_points():
     assert lib.sage_workspace_layout(1, 2, 300, offs) == 11
     vals = list(offs)
     # every segment starts on a 256-byte boundary; the status word (entry 10) is a spare word of
-    # the control block (entry 9), cleared by the same memset
+    # the control block (entry 9), cleared by the same kernel
     assert vals == sorted(vals) and all(v % 256 == 0 for i, v in enumerate(vals) if i != 10)
     assert vals[9] < vals[10] < vals[9] + 4096 and vals[10] % 4 == 0
     assert lib.sage_prologue_ctrl_bytes(1, 48, 47520) >= 48 * 12
@@ -73,7 +73,7 @@ def test_extended_entry_points_validate_on_the_host():
     assert lib.sage_workspace_layout_ex(2, 4, 2, 70, 200, offs) == 13
     vals = list(offs)
     # every segment starts on a 256-byte boundary; the status word (entry 10) is a spare word of
-    # the control block (entry 9), cleared by the same memset
+    # the control block (entry 9), cleared by the same kernel
     assert vals == sorted(vals) and all(v % 256 == 0 for i, v in enumerate(vals) if i != 10)
     assert vals[9] < vals[10] < vals[9] + 4096 and vals[10] % 4 == 0
     assert lib.sage_workspace_layout_ex(2, 4, 3, 70, 200, offs) == _native.SAGE_E_ARG

@@ -196,7 +196,7 @@ def test_varlen_matches_per_sequence_calls(dtype, causal):
 
 def test_cuda_graph_capture_and_replay():
     """After one warm-up call (library load, shared-memory opt-in, workspace allocation) the whole
-    call -- memsets, tensor-map encodes on the host, three kernels -- can be captured and replayed."""
+    call -- tensor-map encodes on the host, four kernels -- can be captured and replayed."""
     q, k, v = _inputs(1, 8, 8, 300, 300, torch.float16, 11)
     q, k, v = q.cuda(), k.cuda(), v.cuda()
     want = sageattention.sageattn(q, k, v, is_causal=True)
